@@ -1,0 +1,16 @@
+"""cudadma_b200 -- CudaDMA's object API on Blackwell (sm_100a).
+
+The device library is header-only (include/cudadma/cudadma.h); this package
+holds the kernels built on it, their C ABI (libcudadma_b200.so) and the thin
+host layer over that ABI.
+"""
+from .capi import (CudaDMAError, IMPL_NATIVE, IMPL_PORTABLE, LIB_PATH, STENCIL_COEFFS, SYMBOLS, device_status,
+                   gather_scatter, gather_scatter_host, launch_count, lib, release_workspace, seq_copy, seq_copy_host,
+                   stencil25_run, stencil25_run_host, stencil25_step, strided_transpose, strided_transpose_host,
+                   version)
+
+__all__ = [
+    "CudaDMAError", "IMPL_NATIVE", "IMPL_PORTABLE", "LIB_PATH", "STENCIL_COEFFS", "SYMBOLS", "device_status",
+    "gather_scatter", "gather_scatter_host", "launch_count", "lib", "release_workspace", "seq_copy", "seq_copy_host",
+    "stencil25_run", "stencil25_run_host", "stencil25_step", "strided_transpose", "strided_transpose_host", "version",
+]

@@ -1,0 +1,202 @@
+"""ctypes binding of libcudadma_b200.so (declarations: include/cudadma_b200.h).
+
+The library is the product; this module only loads it and checks arguments and
+status codes. There is no CPU fallback: a missing library raises at first use,
+and every compute call needs a CUDA device.
+
+Tensors are torch CUDA tensors (torch supplies device memory and streams);
+raw integer device addresses are accepted too.
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libcudadma_b200.so")
+
+OK, ERR_ARG, ERR_CUDA, ERR_UNSUPPORTED, ERR_NOMEM, ERR_TIMEOUT = 0, -1, -2, -3, -4, 1
+IMPL_NATIVE, IMPL_PORTABLE = 0, 1
+_IMPLS = {"native": IMPL_NATIVE, "portable": IMPL_PORTABLE, IMPL_NATIVE: IMPL_NATIVE, IMPL_PORTABLE: IMPL_PORTABLE}
+
+# every symbol include/cudadma_b200.h declares: (name, restype, argtypes)
+_c = ctypes
+SYMBOLS = [
+    ("cudadma_version", _c.c_int, []),
+    ("cudadma_status_string", _c.c_char_p, [_c.c_int]),
+    ("cudadma_last_cuda_error", _c.c_int, []),
+    ("cudadma_device_status", _c.c_int, [_c.c_void_p, _c.POINTER(_c.c_uint)]),
+    ("cudadma_launch_count", _c.c_ulonglong, []),
+    ("cudadma_seq_copy", _c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_int, _c.c_int, _c.c_void_p]),
+    ("cudadma_strided_transpose", _c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.c_void_p]),
+    ("cudadma_gather_scatter", _c.c_int,
+     [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_int, _c.c_int, _c.c_void_p]),
+    ("cudadma_stencil25_step", _c.c_int,
+     [_c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.POINTER(_c.c_float), _c.c_int,
+      _c.c_int, _c.c_void_p]),
+    ("cudadma_stencil25_run", _c.c_int,
+     [_c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.POINTER(_c.c_float), _c.c_int, _c.c_int,
+      _c.c_void_p]),
+    ("cudadma_seq_copy_host", _c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_int, _c.c_int]),
+    ("cudadma_strided_transpose_host", _c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int]),
+    ("cudadma_gather_scatter_host", _c.c_int,
+     [_c.c_void_p, _c.c_size_t, _c.c_void_p, _c.c_size_t, _c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_int, _c.c_int]),
+    ("cudadma_stencil25_run_host", _c.c_int,
+     [_c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.POINTER(_c.c_float), _c.c_int, _c.c_int]),
+    ("cudadma_release_workspace", _c.c_int, []),
+]
+
+# the benchmark's stencil coefficients c0..c4
+STENCIL_COEFFS = (-2.847, 1.6, -0.2, 0.0254, -0.00179)
+
+_lib = None
+
+
+class CudaDMAError(RuntimeError):
+    def __init__(self, call, status, detail=""):
+        self.status = status
+        super().__init__("%s failed with status %d (%s)%s" % (call, status, detail, ""))
+
+
+def lib():
+    """The loaded library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                "%s is missing: build it with `python -c 'import __graft_entry__ as g; g.build()'` "
+                "(there is no CPU fallback)" % LIB_PATH)
+        l = ctypes.CDLL(LIB_PATH)
+        for name, res, args in SYMBOLS:
+            fn = getattr(l, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = l
+    return _lib
+
+
+def _check(call, status):
+    if status != OK:
+        l = lib()
+        detail = l.cudadma_status_string(status).decode()
+        if status == ERR_CUDA:
+            detail += ", cudaError %d" % l.cudadma_last_cuda_error()
+        raise CudaDMAError(call, status, detail)
+
+
+def _ptr(x):
+    if x is None:
+        return None
+    if isinstance(x, int):
+        return x
+    if hasattr(x, "data_ptr"):  # torch tensor
+        return x.data_ptr()
+    if hasattr(x, "ctypes"):  # numpy array (host-buffer forms)
+        return x.ctypes.data
+    raise TypeError("expected a tensor, an array or an address, got %r" % type(x))
+
+
+def _stream(stream):
+    if stream is None:
+        import torch
+        return torch.cuda.current_stream().cuda_stream
+    if isinstance(stream, int):
+        return stream
+    return stream.cuda_stream
+
+
+def _coeffs(coeff):
+    coeff = STENCIL_COEFFS if coeff is None else coeff
+    if len(coeff) != 5:
+        raise ValueError("the stencil takes five coefficients c0..c4")
+    return (ctypes.c_float * 5)(*[float(c) for c in coeff])
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if hasattr(t, "is_cuda") and not t.is_cuda:
+            raise ValueError("device calls take CUDA tensors; use the *_host form for host memory")
+        if hasattr(t, "is_contiguous") and not t.is_contiguous():
+            raise ValueError("tensors must be contiguous")
+
+
+def version():
+    return lib().cudadma_version()
+
+
+def launch_count():
+    return int(lib().cudadma_launch_count())
+
+
+def device_status(stream=None):
+    """Reads and clears the device status word (0 = no wait gave up). Synchronises the stream."""
+    out = ctypes.c_uint(0)
+    _check("cudadma_device_status", lib().cudadma_device_status(_stream(stream), ctypes.byref(out)))
+    return out.value
+
+
+def seq_copy(dst, src, nbytes=None, chunk_bytes=16384, impl="native", stream=None):
+    _require_cuda(dst, src)
+    if nbytes is None:
+        nbytes = src.numel() * src.element_size()
+    _check("cudadma_seq_copy",
+           lib().cudadma_seq_copy(_ptr(dst), _ptr(src), nbytes, chunk_bytes, _IMPLS[impl], _stream(stream)))
+
+
+def strided_transpose(dst, src, rows, cols, impl="native", stream=None):
+    _require_cuda(dst, src)
+    _check("cudadma_strided_transpose",
+           lib().cudadma_strided_transpose(_ptr(dst), _ptr(src), rows, cols, _IMPLS[impl], _stream(stream)))
+
+
+def gather_scatter(out, table, gather_idx, scatter_idx, n=None, record_bytes=32, impl="native", stream=None):
+    _require_cuda(out, table, gather_idx, scatter_idx)
+    if n is None:
+        n = gather_idx.numel()
+    _check("cudadma_gather_scatter",
+           lib().cudadma_gather_scatter(_ptr(out), _ptr(table), _ptr(gather_idx), _ptr(scatter_idx), n, record_bytes,
+                                        _IMPLS[impl], _stream(stream)))
+
+
+def stencil25_step(out, inp, nx, ny, nz, z_begin=0, z_end=None, coeff=None, z_chunk=0, impl="native", stream=None):
+    _require_cuda(out, inp)
+    if z_end is None:
+        z_end = nz
+    _check("cudadma_stencil25_step",
+           lib().cudadma_stencil25_step(_ptr(out), _ptr(inp), nx, ny, nz, z_begin, z_end, _coeffs(coeff), z_chunk,
+                                        _IMPLS[impl], _stream(stream)))
+
+
+def stencil25_run(a, b, nx, ny, nz, steps, coeff=None, impl="native", stream=None):
+    """`steps` ping-pong steps starting from `a`; returns the tensor that holds the result."""
+    _require_cuda(a, b)
+    _check("cudadma_stencil25_run",
+           lib().cudadma_stencil25_run(_ptr(a), _ptr(b), nx, ny, nz, _coeffs(coeff), steps, _IMPLS[impl],
+                                       _stream(stream)))
+    return a if steps % 2 == 0 else b
+
+
+# ---- host-buffer forms (numpy arrays or pinned CPU tensors) ----
+
+def seq_copy_host(h_dst, h_src, nbytes, chunk_bytes=16384, impl="native"):
+    _check("cudadma_seq_copy_host",
+           lib().cudadma_seq_copy_host(_ptr(h_dst), _ptr(h_src), nbytes, chunk_bytes, _IMPLS[impl]))
+
+
+def strided_transpose_host(h_dst, h_src, rows, cols, impl="native"):
+    _check("cudadma_strided_transpose_host",
+           lib().cudadma_strided_transpose_host(_ptr(h_dst), _ptr(h_src), rows, cols, _IMPLS[impl]))
+
+
+def gather_scatter_host(h_out, out_records, h_table, table_records, h_gather_idx, h_scatter_idx, n, record_bytes=32,
+                        impl="native"):
+    _check("cudadma_gather_scatter_host",
+           lib().cudadma_gather_scatter_host(_ptr(h_out), out_records, _ptr(h_table), table_records,
+                                             _ptr(h_gather_idx), _ptr(h_scatter_idx), n, record_bytes, _IMPLS[impl]))
+
+
+def stencil25_run_host(h_out, h_in, nx, ny, nz, steps, coeff=None, impl="native"):
+    _check("cudadma_stencil25_run_host",
+           lib().cudadma_stencil25_run_host(_ptr(h_out), _ptr(h_in), nx, ny, nz, _coeffs(coeff), steps, _IMPLS[impl]))
+
+
+def release_workspace():
+    _check("cudadma_release_workspace", lib().cudadma_release_workspace())

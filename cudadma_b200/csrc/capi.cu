@@ -1,0 +1,382 @@
+/*
+ * capi.cu -- host side of libcudadma_b200.so: argument checks, tensor-map
+ * encoding, launches, the host-buffer forms and their device workspace.
+ * Declarations and the reference programs each entry point replaces are in
+ * include/cudadma_b200.h.
+ */
+#include "cudadma_b200.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <mutex>
+
+#include "cudadma.h"
+#include "common_kernels.cuh"
+#include "dma_kernels.cuh"
+#include "portable_kernels.cuh"
+#include "stencil25.cuh"
+
+namespace {
+
+thread_local int t_last_cuda_error = 0;
+std::atomic<unsigned long long> g_launches{0};
+
+#define CK(call)                                   \
+  do {                                             \
+    cudaError_t e_ = (call);                       \
+    if (e_ != cudaSuccess) {                       \
+      t_last_cuda_error = (int)e_;                 \
+      return CUDADMA_ERR_CUDA;                     \
+    }                                              \
+  } while (0)
+
+int launched() {
+  ++g_launches;
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    t_last_cuda_error = (int)e;
+    return CUDADMA_ERR_CUDA;
+  }
+  return CUDADMA_OK;
+}
+
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) n = 0;
+  }
+  return n;
+}
+
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+/* cuTensorMapEncodeTiled is fetched through the runtime so that the library
+ * has no link-time dependency on the driver library and loads on a machine
+ * without a GPU. */
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+/* fp32 tensor map, `rank` dims (x fastest), zero fill outside the tensor */
+int make_map_f32(CUtensorMap *map, const void *base, int rank, const cuuint64_t *dims, const cuuint64_t *strides_bytes,
+                 const cuuint32_t *box, CUtensorMapSwizzle swizzle) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) { t_last_cuda_error = (int)cudaErrorNotSupported; return CUDADMA_ERR_CUDA; }
+  cuuint32_t ones[5] = {1, 1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<void *>(base), dims,
+                  strides_bytes, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { t_last_cuda_error = (int)cudaErrorInvalidValue; return CUDADMA_ERR_CUDA; }
+  return CUDADMA_OK;
+}
+
+template <typename K>
+int allow_smem(K kernel, int bytes) {
+  CK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  return CUDADMA_OK;
+}
+
+/* ---- grow-only device workspace for the host-buffer forms ---- */
+std::mutex g_ws_mutex;
+void *g_ws[4] = {nullptr, nullptr, nullptr, nullptr};
+size_t g_ws_bytes[4] = {0, 0, 0, 0};
+cudaStream_t g_ws_stream = nullptr;
+
+int ws_get(int slot, size_t bytes, void **out) {
+  if (g_ws_bytes[slot] < bytes) {
+    if (g_ws[slot]) cudaFree(g_ws[slot]);
+    g_ws[slot] = nullptr; g_ws_bytes[slot] = 0;
+    cudaError_t e = cudaMalloc(&g_ws[slot], bytes);
+    if (e != cudaSuccess) { t_last_cuda_error = (int)e; cudaGetLastError(); return CUDADMA_ERR_NOMEM; }
+    g_ws_bytes[slot] = bytes;
+  }
+  *out = g_ws[slot];
+  return CUDADMA_OK;
+}
+int ws_stream(cudaStream_t *s) {
+  if (!g_ws_stream) CK(cudaStreamCreateWithFlags(&g_ws_stream, cudaStreamNonBlocking));
+  *s = g_ws_stream;
+  return CUDADMA_OK;
+}
+
+int finish_status(cudaStream_t s) {
+  unsigned int w = 0;
+  CK(cudadma_b200::read_status(&w, s));
+  return w ? CUDADMA_ERR_TIMEOUT : CUDADMA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int cudadma_version(void) { return 100; }
+
+const char *cudadma_status_string(int status) {
+  switch (status) {
+    case CUDADMA_OK: return "ok";
+    case CUDADMA_ERR_ARG: return "invalid argument";
+    case CUDADMA_ERR_CUDA: return "CUDA call failed";
+    case CUDADMA_ERR_UNSUPPORTED: return "implementation not available";
+    case CUDADMA_ERR_NOMEM: return "out of device or pinned memory";
+    case CUDADMA_ERR_TIMEOUT: return "a bounded wait inside the kernel gave up";
+    default: return "unknown status";
+  }
+}
+int cudadma_last_cuda_error(void) { return t_last_cuda_error; }
+unsigned long long cudadma_launch_count(void) { return g_launches.load(); }
+
+int cudadma_device_status(void *stream, unsigned int *out) {
+  if (!out) return CUDADMA_ERR_ARG;
+  CK(cudadma_b200::read_status(out, (cudaStream_t)stream));
+  return CUDADMA_OK;
+}
+
+int cudadma_seq_copy(void *dst, const void *src, size_t bytes, int chunk_bytes, int impl, void *stream) {
+  using namespace cudadma_b200::kernels;
+  if (!dst || !src || (bytes & 3) || chunk_bytes < 16 || chunk_bytes > 16384 || (chunk_bytes & 15) ||
+      !aligned16(dst) || !aligned16(src))
+    return CUDADMA_ERR_ARG;
+  if (bytes == 0) return CUDADMA_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int sms = sm_count();
+  if (sms <= 0) { t_last_cuda_error = (int)cudaErrorNoDevice; return CUDADMA_ERR_CUDA; }
+  const long long nfull = (long long)(bytes / (size_t)chunk_bytes);
+  const int tail = (int)(bytes - (size_t)nfull * chunk_bytes);
+  char *d = static_cast<char *>(dst);
+  const char *p = static_cast<const char *>(src);
+  if (nfull > 0) {
+    if (impl == CUDADMA_IMPL_NATIVE && chunk_bytes == 16384) {
+      constexpr int STAGES = 8;
+      auto k = seq_copy_kernel<16384, STAGES, true>;
+      if (int r = allow_smem(k, STAGES * 16384)) return r;
+      const int grid = (int)(nfull < sms ? nfull : sms);
+      k<<<grid, SEQ_DMA_THREADS + SEQ_COMPUTE_THREADS, STAGES * 16384, s>>>(d, p, nfull);
+      if (int r = launched()) return r;
+    } else if (impl == CUDADMA_IMPL_PORTABLE && chunk_bytes == 16384) {
+      if (int r = portable::launch_seq_copy(d, p, nfull, sms, s)) { t_last_cuda_error = r; return CUDADMA_ERR_CUDA; }
+      ++g_launches;
+    } else if (impl == CUDADMA_IMPL_NATIVE || impl == CUDADMA_IMPL_PORTABLE) {
+      const long long want = 4ll * sms;
+      const int grid = (int)(nfull < want ? nfull : want);
+      seq_copy_runtime_kernel<<<grid, SEQ_DMA_THREADS + SEQ_COMPUTE_THREADS, chunk_bytes, s>>>(d, p, nfull, chunk_bytes);
+      if (int r = launched()) return r;
+    } else {
+      return CUDADMA_ERR_UNSUPPORTED;
+    }
+  }
+  if (tail > 0) {
+    seq_copy_runtime_kernel<<<1, SEQ_DMA_THREADS + SEQ_COMPUTE_THREADS, tail, s>>>(
+        d + (size_t)nfull * chunk_bytes, p + (size_t)nfull * chunk_bytes, 1, tail);
+    if (int r = launched()) return r;
+  }
+  return CUDADMA_OK;
+}
+
+int cudadma_strided_transpose(float *dst, const float *src, int rows, int cols, int impl, void *stream) {
+  using namespace cudadma_b200::kernels;
+  if (!dst || !src || rows <= 0 || cols <= 0 || (rows % TR_TILE_ROWS) || (cols % TR_TILE_COLS) || !aligned16(dst) ||
+      !aligned16(src))
+    return CUDADMA_ERR_ARG;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int sms = sm_count();
+  if (sms <= 0) { t_last_cuda_error = (int)cudaErrorNoDevice; return CUDADMA_ERR_CUDA; }
+  const long long ntiles = (long long)(rows / TR_TILE_ROWS) * (cols / TR_TILE_COLS);
+  if (impl == CUDADMA_IMPL_NATIVE) {
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * 4};
+    const cuuint32_t box[2] = {TR_BOX_COLS, TR_TILE_ROWS};
+    if (int r = make_map_f32(&map, src, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return r;
+    constexpr int STAGES = 6;
+    constexpr int SMEM = STAGES * TR_TILE_BYTES + 1024;
+    auto k = transpose_kernel<STAGES>;
+    if (int r = allow_smem(k, SMEM)) return r;
+    const int grid = (int)(ntiles < sms ? ntiles : sms);
+    k<<<grid, TR_DMA_THREADS + TR_COMPUTE_THREADS, SMEM, s>>>(map, dst, rows, cols, cols * 4);
+    return launched();
+  }
+  if (impl == CUDADMA_IMPL_PORTABLE) {
+    if (int r = portable::launch_transpose(dst, src, rows, cols, sms, s)) { t_last_cuda_error = r; return CUDADMA_ERR_CUDA; }
+    ++g_launches;
+    return CUDADMA_OK;
+  }
+  return CUDADMA_ERR_UNSUPPORTED;
+}
+
+int cudadma_gather_scatter(void *out, const void *table, const int32_t *gather_idx, const int32_t *scatter_idx,
+                           size_t n, int record_bytes, int impl, void *stream) {
+  using namespace cudadma_b200::kernels;
+  if (!out || !table || !gather_idx || !scatter_idx || record_bytes != 32 || (n % 128) || !aligned16(out) ||
+      !aligned16(table) || !aligned16(gather_idx) || !aligned16(scatter_idx))
+    return CUDADMA_ERR_ARG;
+  if (n == 0) return CUDADMA_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int sms = sm_count();
+  if (sms <= 0) { t_last_cuda_error = (int)cudaErrorNoDevice; return CUDADMA_ERR_CUDA; }
+  const long long nbuf = (long long)(n / 128);
+  if (impl == CUDADMA_IMPL_NATIVE) {
+    constexpr int STAGES = 8;
+    constexpr int SMEM = STAGES * 128 * 32;
+    auto k = gather_scatter_kernel<32, 128, STAGES>;
+    const long long want = 4ll * sms;
+    const int grid = (int)(nbuf < want ? nbuf : want);
+    k<<<grid, GS_THREADS, SMEM, s>>>(static_cast<char *>(out), static_cast<const char *>(table), gather_idx,
+                                     scatter_idx, nbuf);
+    return launched();
+  }
+  if (impl == CUDADMA_IMPL_PORTABLE) {
+    if (int r = portable::launch_gather_scatter(static_cast<char *>(out), static_cast<const char *>(table),
+                                                gather_idx, scatter_idx, nbuf, sms, s)) {
+      t_last_cuda_error = r;
+      return CUDADMA_ERR_CUDA;
+    }
+    ++g_launches;
+    return CUDADMA_OK;
+  }
+  return CUDADMA_ERR_UNSUPPORTED;
+}
+
+int cudadma_stencil25_step(float *out, const float *in, int nx, int ny, int nz, int z_begin, int z_end,
+                           const float coeff[5], int z_chunk, int impl, void *stream) {
+  if (!out || !in || !coeff || nx <= 0 || ny <= 0 || nz <= 0 || (nx & 3) || z_begin < 0 || z_end > nz ||
+      z_begin > z_end || !aligned16(out) || !aligned16(in) || out == in)
+    return CUDADMA_ERR_ARG;
+  if (z_begin == z_end) return CUDADMA_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int sms = sm_count();
+  if (sms <= 0) { t_last_cuda_error = (int)cudaErrorNoDevice; return CUDADMA_ERR_CUDA; }
+  stencil25::Coeffs k;
+  for (int i = 0; i < 5; ++i) k.c[i] = coeff[i];
+  const int tiles_x = (nx + stencil25::TILE_X - 1) / stencil25::TILE_X;
+  const int tiles_y = (ny + stencil25::TILE_Y - 1) / stencil25::TILE_Y;
+  const int depth = z_end - z_begin;
+  if (z_chunk <= 0) {
+    /* enough CTAs for a few waves over the SMs, but runs of at least 32 planes so that the
+     * eight lead-in/lead-out planes of a run stay a small share of its loads */
+    const long long tiles = (long long)tiles_x * tiles_y;
+    const long long want = 24ll * sms;
+    long long chunks = (want + tiles - 1) / tiles;
+    if (chunks < 1) chunks = 1;
+    z_chunk = (int)((depth + chunks - 1) / chunks);
+    if (z_chunk < 32) z_chunk = 32;
+    if (z_chunk > depth) z_chunk = depth;
+  }
+  const int zc = (depth + z_chunk - 1) / z_chunk;
+  if (zc > 65535 || tiles_y > 65535) return CUDADMA_ERR_ARG;
+  if (impl == CUDADMA_IMPL_NATIVE) {
+    CUtensorMap map;
+    const cuuint64_t dims[3] = {(cuuint64_t)nx, (cuuint64_t)ny, (cuuint64_t)nz};
+    const cuuint64_t strides[2] = {(cuuint64_t)nx * 4, (cuuint64_t)nx * ny * 4};
+    const cuuint32_t box[3] = {stencil25::WIN_X, stencil25::WIN_Y, 1};
+    if (int r = make_map_f32(&map, in, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return r;
+    dim3 grid(tiles_x, tiles_y, zc);
+    stencil25::tensor_kernel<<<grid, stencil25::COMPUTE_THREADS + stencil25::DMA_THREADS, stencil25::SMEM_BYTES, s>>>(
+        map, out, nx, ny, z_begin, z_end, z_chunk, k);
+    return launched();
+  }
+  return CUDADMA_ERR_UNSUPPORTED;
+}
+
+int cudadma_stencil25_run(float *a, float *b, int nx, int ny, int nz, const float coeff[5], int steps, int impl,
+                          void *stream) {
+  if (steps < 0) return CUDADMA_ERR_ARG;
+  float *cur = a, *nxt = b;
+  for (int t = 0; t < steps; ++t) {
+    if (int r = cudadma_stencil25_step(nxt, cur, nx, ny, nz, 0, nz, coeff, 0, impl, stream)) return r;
+    float *tmp = cur; cur = nxt; nxt = tmp;
+  }
+  return CUDADMA_OK;
+}
+
+/* ---- host-buffer forms ---- */
+
+int cudadma_seq_copy_host(void *h_dst, const void *h_src, size_t bytes, int chunk_bytes, int impl) {
+  if (!h_dst || !h_src) return CUDADMA_ERR_ARG;
+  std::lock_guard<std::mutex> lock(g_ws_mutex);
+  cudaStream_t s; void *din, *dout;
+  if (int r = ws_stream(&s)) return r;
+  if (int r = ws_get(0, bytes, &din)) return r;
+  if (int r = ws_get(1, bytes, &dout)) return r;
+  CK(cudaMemcpyAsync(din, h_src, bytes, cudaMemcpyHostToDevice, s));
+  if (int r = cudadma_seq_copy(dout, din, bytes, chunk_bytes, impl, s)) return r;
+  CK(cudaMemcpyAsync(h_dst, dout, bytes, cudaMemcpyDeviceToHost, s));
+  return finish_status(s);
+}
+
+int cudadma_strided_transpose_host(float *h_dst, const float *h_src, int rows, int cols, int impl) {
+  if (!h_dst || !h_src || rows <= 0 || cols <= 0) return CUDADMA_ERR_ARG;
+  const size_t bytes = (size_t)rows * cols * 4;
+  std::lock_guard<std::mutex> lock(g_ws_mutex);
+  cudaStream_t s; void *din, *dout;
+  if (int r = ws_stream(&s)) return r;
+  if (int r = ws_get(0, bytes, &din)) return r;
+  if (int r = ws_get(1, bytes, &dout)) return r;
+  CK(cudaMemcpyAsync(din, h_src, bytes, cudaMemcpyHostToDevice, s));
+  if (int r = cudadma_strided_transpose((float *)dout, (const float *)din, rows, cols, impl, s)) return r;
+  CK(cudaMemcpyAsync(h_dst, dout, bytes, cudaMemcpyDeviceToHost, s));
+  return finish_status(s);
+}
+
+int cudadma_gather_scatter_host(void *h_out, size_t out_records, const void *h_table, size_t table_records,
+                                const int32_t *h_gather_idx, const int32_t *h_scatter_idx, size_t n,
+                                int record_bytes, int impl) {
+  if (!h_out || !h_table || !h_gather_idx || !h_scatter_idx || record_bytes <= 0) return CUDADMA_ERR_ARG;
+  std::lock_guard<std::mutex> lock(g_ws_mutex);
+  cudaStream_t s; void *dtab, *dout, *dg, *ds;
+  if (int r = ws_stream(&s)) return r;
+  if (int r = ws_get(0, table_records * record_bytes, &dtab)) return r;
+  if (int r = ws_get(1, out_records * record_bytes, &dout)) return r;
+  if (int r = ws_get(2, n * 4, &dg)) return r;
+  if (int r = ws_get(3, n * 4, &ds)) return r;
+  CK(cudaMemcpyAsync(dtab, h_table, table_records * record_bytes, cudaMemcpyHostToDevice, s));
+  CK(cudaMemcpyAsync(dg, h_gather_idx, n * 4, cudaMemcpyHostToDevice, s));
+  CK(cudaMemcpyAsync(ds, h_scatter_idx, n * 4, cudaMemcpyHostToDevice, s));
+  /* slots no index names keep the caller's bytes */
+  CK(cudaMemcpyAsync(dout, h_out, out_records * record_bytes, cudaMemcpyHostToDevice, s));
+  if (int r = cudadma_gather_scatter(dout, dtab, (const int32_t *)dg, (const int32_t *)ds, n, record_bytes, impl, s))
+    return r;
+  CK(cudaMemcpyAsync(h_out, dout, out_records * record_bytes, cudaMemcpyDeviceToHost, s));
+  return finish_status(s);
+}
+
+int cudadma_stencil25_run_host(float *h_out, const float *h_in, int nx, int ny, int nz, const float coeff[5],
+                               int steps, int impl) {
+  if (!h_out || !h_in || nx <= 0 || ny <= 0 || nz <= 0) return CUDADMA_ERR_ARG;
+  const size_t bytes = (size_t)nx * ny * nz * 4;
+  std::lock_guard<std::mutex> lock(g_ws_mutex);
+  cudaStream_t s; void *da, *db;
+  if (int r = ws_stream(&s)) return r;
+  if (int r = ws_get(0, bytes, &da)) return r;
+  if (int r = ws_get(1, bytes, &db)) return r;
+  CK(cudaMemcpyAsync(da, h_in, bytes, cudaMemcpyHostToDevice, s));
+  if (int r = cudadma_stencil25_run((float *)da, (float *)db, nx, ny, nz, coeff, steps, impl, s)) return r;
+  CK(cudaMemcpyAsync(h_out, (steps & 1) ? db : da, bytes, cudaMemcpyDeviceToHost, s));
+  return finish_status(s);
+}
+
+int cudadma_release_workspace(void) {
+  std::lock_guard<std::mutex> lock(g_ws_mutex);
+  for (int i = 0; i < 4; ++i) {
+    if (g_ws[i]) cudaFree(g_ws[i]);
+    g_ws[i] = nullptr; g_ws_bytes[i] = 0;
+  }
+  return CUDADMA_OK;
+}
+
+}  /* extern "C" */

@@ -1,0 +1,188 @@
+/*
+ * dma_kernels.cuh -- sequential chunk copy and strided tile transpose as
+ * persistent kernels built on the CudaDMA objects of cudadma.h, using the
+ * sm_100a extensions (multi-stage rings of objects, tensor-map tile loads,
+ * bulk stores). The gather + scatter kernel needs no extension and lives in
+ * common_kernels.cuh.
+ *
+ * Loop structure follows the reference's throughput benchmark
+ * (src/perf/sequential/perf_sequential.cu:79-114): a CTA walks its share of
+ * the units, DMA warps fill shared-memory buffers, compute warps drain them.
+ */
+#ifndef CUDADMA_B200_DMA_KERNELS_CUH
+#define CUDADMA_B200_DMA_KERNELS_CUH
+
+#include "cudadma.h"
+#include "common_kernels.cuh"
+
+namespace cudadma_b200 {
+namespace kernels {
+
+/* ------------------------------------------------------------------------ */
+/* Sequential: CHUNK-byte chunks global -> shared -> global.                 */
+/* 4 DMA warps + 8 compute warps; STAGES buffers in flight per CTA.          */
+/* Chunk c of the array is handled by CTA c % gridDim.x.                     */
+/* BULK_STORE: one compute thread writes a chunk back with a bulk store;     */
+/* otherwise all compute threads copy it with 16-byte loads and stores.      */
+/* ------------------------------------------------------------------------ */
+constexpr int SEQ_DMA_THREADS = 128;
+constexpr int SEQ_COMPUTE_THREADS = 256;
+
+template <int CHUNK, int STAGES, bool BULK_STORE>
+__global__ void __launch_bounds__(SEQ_DMA_THREADS + SEQ_COMPUTE_THREADS, 1)
+seq_copy_kernel(char *__restrict__ dst, const char *__restrict__ src, const long long nchunks) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  typedef CudaDMASequential<true, 16, 64, CHUNK, SEQ_DMA_THREADS> Dma;
+  Ring<Dma, STAGES> ring(SEQ_COMPUTE_THREADS, SEQ_COMPUTE_THREADS);
+  const long long stride = gridDim.x;
+
+  if (ring.stage[0].owns_this_thread()) {
+    for (long long c0 = blockIdx.x;; c0 += stride * STAGES) {
+#pragma unroll
+      for (int s = 0; s < STAGES; ++s) {
+        const long long c = c0 + s * stride;
+        if (c >= nchunks) return;
+        ring.stage[s].execute_dma(src + c * CHUNK, smem + s * CHUNK);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) ring.stage[s].start_async_dma();
+    bool more = true;
+    for (long long c0 = blockIdx.x; more; c0 += stride * STAGES) {
+#pragma unroll
+      for (int s = 0; s < STAGES; ++s) {
+        const long long c = c0 + s * stride;
+        if (c >= nchunks) { more = false; break; }
+        ring.stage[s].wait_for_dma_finish();
+        if (BULK_STORE) {
+          if (threadIdx.x == 0) {
+            ptx::bulk_s2g(dst + c * CHUNK, ptx::smem_u32(smem + s * CHUNK), CHUNK);
+            ptx::bulk_commit();
+            ptx::bulk_wait_read<0>();
+          }
+        } else {
+          const uint4 *b = reinterpret_cast<const uint4 *>(smem + s * CHUNK);
+          uint4 *o = reinterpret_cast<uint4 *>(dst + c * CHUNK);
+#pragma unroll
+          for (int i = threadIdx.x; i < CHUNK / 16; i += SEQ_COMPUTE_THREADS) o[i] = b[i];
+        }
+        ring.stage[s].start_async_dma();
+      }
+    }
+    if (BULK_STORE && threadIdx.x == 0) ptx::bulk_wait<0>();
+  }
+}
+
+/* Same loop for a chunk size known only at run time (used for the last,
+ * shorter chunk and for odd chunk sizes); single buffer. */
+__global__ void __launch_bounds__(SEQ_DMA_THREADS + SEQ_COMPUTE_THREADS, 1)
+seq_copy_runtime_kernel(char *__restrict__ dst, const char *__restrict__ src, const long long nchunks,
+                        const int chunk_bytes) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  CudaDMASequential<true, 4, 16> dma(0, SEQ_DMA_THREADS, SEQ_COMPUTE_THREADS, SEQ_COMPUTE_THREADS, chunk_bytes);
+  if (dma.owns_this_thread()) {
+    for (long long c = blockIdx.x; c < nchunks; c += gridDim.x) dma.execute_dma(src + c * chunk_bytes, smem);
+  } else {
+    dma.start_async_dma();
+    for (long long c = blockIdx.x; c < nchunks; c += gridDim.x) {
+      dma.wait_for_dma_finish();
+      const unsigned int *b = reinterpret_cast<const unsigned int *>(smem);
+      unsigned int *o = reinterpret_cast<unsigned int *>(dst + c * chunk_bytes);
+      for (int i = threadIdx.x; i < chunk_bytes / 4; i += SEQ_COMPUTE_THREADS) o[i] = b[i];
+      dma.start_async_dma();
+    }
+  }
+}
+
+/* ------------------------------------------------------------------------ */
+/* Strided: 128-row x 64-column fp32 tiles (row pitch = matrix width) pulled  */
+/* into shared memory by CudaDMAStrided through a tensor map, written back    */
+/* transposed: out[c * rows + r] = in[r * cols + c].                          */
+/* The tile arrives as two 128 x 32 boxes in the 128-byte-swizzle layout:     */
+/* element (r, c) of a box sits at r*128 + 16*((c/4) ^ (r%8)) + 4*(c%4), so   */
+/* a quarter-warp reading one 16-byte column chunk of eight consecutive rows  */
+/* touches eight different bank groups. Lane l then owns rows 4l..4l+3 of a   */
+/* 4-column chunk, transposes the 4x4 block in registers and stores four      */
+/* 16-byte pieces, one per output row: 512 contiguous bytes per warp store.   */
+/* ------------------------------------------------------------------------ */
+constexpr int TR_TILE_ROWS = 128, TR_TILE_COLS = 64, TR_BOX_COLS = 32;
+constexpr int TR_DMA_THREADS = 32, TR_COMPUTE_THREADS = 256;
+constexpr int TR_TILE_BYTES = TR_TILE_ROWS * TR_TILE_COLS * 4;
+constexpr int TR_BOX_BYTES = TR_TILE_ROWS * TR_BOX_COLS * 4;
+
+template <int STAGES>
+__global__ void __launch_bounds__(TR_DMA_THREADS + TR_COMPUTE_THREADS, 1)
+transpose_kernel(const __grid_constant__ CUtensorMap in_map, float *__restrict__ out, const int rows,
+                 const int cols, const int src_pitch_bytes) {
+  extern __shared__ unsigned char smem_raw[];
+  /* the 128-byte swizzle pattern repeats every 1024 bytes: align the ring to it */
+  unsigned char *smem = reinterpret_cast<unsigned char *>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  typedef CudaDMAStrided<true, 16, 64, TR_TILE_COLS * 4, TR_DMA_THREADS, TR_TILE_ROWS> Dma;
+  Ring<Dma, STAGES> ring(TR_COMPUTE_THREADS, TR_COMPUTE_THREADS, src_pitch_bytes, TR_TILE_COLS * 4);
+  const int tiles_x = cols / TR_TILE_COLS;
+  const long long ntiles = (long long)tiles_x * (rows / TR_TILE_ROWS);
+  const long long stride = gridDim.x;
+
+  if (ring.stage[0].owns_this_thread()) {
+    for (long long t0 = blockIdx.x;; t0 += stride * STAGES) {
+#pragma unroll
+      for (int s = 0; s < STAGES; ++s) {
+        const long long t = t0 + s * stride;
+        if (t >= ntiles) return;
+        const int ty = (int)(t / tiles_x), tx = (int)(t - (long long)ty * tiles_x);
+        ring.stage[s].execute_dma_tensor(&in_map, tx * TR_TILE_COLS, ty * TR_TILE_ROWS, smem + s * TR_TILE_BYTES,
+                                         TR_TILE_COLS / TR_BOX_COLS, TR_BOX_COLS, TR_BOX_BYTES);
+      }
+    }
+  } else {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    /* rotation that makes the four row loads of a lane conflict-free: in a quarter-warp the
+     * rows 4l + ((i + l/2) % 4) take all eight values mod 8 */
+    const int rot = (lane >> 1) & 3;
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) ring.stage[s].start_async_dma();
+    bool more = true;
+    for (long long t0 = blockIdx.x; more; t0 += stride * STAGES) {
+#pragma unroll
+      for (int s = 0; s < STAGES; ++s) {
+        const long long t = t0 + s * stride;
+        if (t >= ntiles) { more = false; break; }
+        const int ty = (int)(t / tiles_x), tx = (int)(t - (long long)ty * tiles_x);
+        ring.stage[s].wait_for_dma_finish();
+        const unsigned char *tile = smem + s * TR_TILE_BYTES;
+#pragma unroll
+        for (int task = warp; task < 16; task += TR_COMPUTE_THREADS / 32) {
+          const int box = task >> 3, k = task & 7;
+          const unsigned char *b = tile + box * TR_BOX_BYTES;
+          float4 v[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int r = 4 * lane + ((i + rot) & 3);
+            v[i] = *reinterpret_cast<const float4 *>(b + r * 128 + 16 * (k ^ (r & 7)));
+          }
+          /* v[i] holds row 4*lane + (i + rot) % 4; put row 4*lane + j into w[j] */
+          float4 w[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int i = (j - rot) & 3;
+            w[j] = (i == 0) ? v[0] : (i == 1) ? v[1] : (i == 2) ? v[2] : v[3];
+          }
+          const long long c0 = (long long)tx * TR_TILE_COLS + box * TR_BOX_COLS + 4 * k;
+          float *o = out + c0 * rows + (long long)ty * TR_TILE_ROWS + 4 * lane;
+          __stcs(reinterpret_cast<float4 *>(o), make_float4(w[0].x, w[1].x, w[2].x, w[3].x));
+          __stcs(reinterpret_cast<float4 *>(o + rows), make_float4(w[0].y, w[1].y, w[2].y, w[3].y));
+          __stcs(reinterpret_cast<float4 *>(o + 2ll * rows), make_float4(w[0].z, w[1].z, w[2].z, w[3].z));
+          __stcs(reinterpret_cast<float4 *>(o + 3ll * rows), make_float4(w[0].w, w[1].w, w[2].w, w[3].w));
+        }
+        ring.stage[s].start_async_dma();
+      }
+    }
+  }
+}
+
+}  // namespace kernels
+}  // namespace cudadma_b200
+
+#endif

@@ -1,0 +1,105 @@
+/*
+ * cudadma_b200.h -- C ABI of libcudadma_b200.so.
+ *
+ * The reference (lightsighter/CudaDMA) is a header-only device library with no
+ * host interface: each of its tests, benchmarks and examples is a main() that
+ * allocates, launches one kernel and checks or times it. These entry points
+ * are that host side as a library: every function states the reference
+ * program whose launch it replaces. A caller binds them with any FFI (plain
+ * pointers and sizes, no C++ types); device pointers are CUDA device
+ * addresses of the current device, `stream` is a cudaStream_t (0 = default).
+ *
+ * Return value: 0 on success, negative for a rejected call, positive when
+ * the kernel ran but a bounded wait inside it gave up.
+ * Nothing here falls back to the CPU: without a CUDA device the compute calls
+ * return CUDADMA_ERR_CUDA.
+ */
+#ifndef CUDADMA_B200_H
+#define CUDADMA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  CUDADMA_OK = 0,
+  CUDADMA_ERR_ARG = -1,         /* null pointer, size not a multiple of what the kernel needs */
+  CUDADMA_ERR_CUDA = -2,        /* a CUDA call failed; see cudadma_last_cuda_error() */
+  CUDADMA_ERR_UNSUPPORTED = -3, /* impl not built into this library */
+  CUDADMA_ERR_NOMEM = -4,       /* device or pinned memory could not be had */
+  CUDADMA_ERR_TIMEOUT = 1       /* a wait inside the kernel gave up; see cudadma_device_status() */
+};
+
+/* Which kernel family runs the workload. */
+enum {
+  CUDADMA_IMPL_NATIVE = 0,   /* sm_100a extensions: object rings, tensor maps, bulk stores */
+  CUDADMA_IMPL_PORTABLE = 1  /* same objects through the reference's API only (double buffered) */
+};
+
+int cudadma_version(void);
+const char *cudadma_status_string(int status);
+/* cudaError_t of the last failed CUDA call of the calling thread, as an int */
+int cudadma_last_cuda_error(void);
+/* Reads and clears the device status word written by a wait that gave up
+ * (bit 31 set | dmaID << 8 | 1 = empty wait, 2 = full wait). Synchronises `stream`. */
+int cudadma_device_status(void *stream, unsigned int *out);
+/* Number of kernels this library has launched in this process (all calls). */
+unsigned long long cudadma_launch_count(void);
+
+/* Sequential chunk copy: dst[0..bytes) = src[0..bytes), every chunk_bytes chunk
+ * staged global -> shared -> global by CudaDMASequential (4 DMA + 8 compute
+ * warps). Replaces the launch in src/perf/sequential/perf_sequential.cu:225-369
+ * (whose kernels only load; the write-back is this benchmark's addition) and
+ * the check of src/tests/test_sequential/cudaDMA_test_sequential_v2.cu:500-512.
+ * bytes % 4 == 0; chunk_bytes % 16 == 0, 16 <= chunk_bytes <= 16384; pointers 16-byte aligned. */
+int cudadma_seq_copy(void *dst, const void *src, size_t bytes, int chunk_bytes, int impl, void *stream);
+
+/* Strided tile transpose: rows x cols fp32 row-major matrix, each 128-row x
+ * 64-column tile pulled by CudaDMAStrided (row pitch = cols) and written back
+ * transposed: dst[c * rows + r] = src[r * cols + c]. The transfer is the one
+ * checked by src/tests/test_strided/cudaDMA_test_strided_v2.cu:659-676.
+ * rows % 128 == 0, cols % 64 == 0; pointers 16-byte aligned. */
+int cudadma_strided_transpose(float *dst, const float *src, int rows, int cols, int impl, void *stream);
+
+/* Indirect gather + scatter: out[scatter_idx[i]] = table[gather_idx[i]] for
+ * records of record_bytes, 128 records per shared buffer: CudaDMAIndirect
+ * gather (src/tests/test_indirect/cudaDMA_test_indirect_v2.cu:661-692) then
+ * CudaDMAIndirect scatter (include/cudaDMAv2.h:14021-14025).
+ * n % 128 == 0; record_bytes == 32; scatter_idx must not repeat. */
+int cudadma_gather_scatter(void *out, const void *table, const int32_t *gather_idx, const int32_t *scatter_idx,
+                           size_t n, int record_bytes, int impl, void *stream);
+
+/* One step of the radius-4 25-point stencil on an nx x ny x nz fp32 grid (x
+ * fastest), output planes [z_begin, z_end) only; reads outside the grid give
+ * zero. 32 x 16 tiles with their halo come in through CudaDMAHalo, z-marching.
+ * The reference has no such kernel; its stencil example
+ * (src/examples/stencil/cudaDMA_stencil2D.cu:60-264) is the launch replaced.
+ * nx % 4 == 0; pointers 16-byte aligned; in and out must not overlap.
+ * z_chunk = planes per CTA (0 = library's choice). */
+int cudadma_stencil25_step(float *out, const float *in, int nx, int ny, int nz, int z_begin, int z_end,
+                           const float coeff[5], int z_chunk, int impl, void *stream);
+/* `steps` ping-pong steps a -> b -> a ...; the result is in a when steps is even, else in b. */
+int cudadma_stencil25_run(float *a, float *b, int nx, int ny, int nz, const float coeff[5], int steps, int impl,
+                          void *stream);
+
+/* Host-buffer forms: the same workloads for callers that hold their data in
+ * host memory. Inputs are copied to the device, the kernel runs, the result
+ * is copied back; the call returns when the result is in h_* memory. Device
+ * staging memory is a grow-only workspace kept by the library
+ * (cudadma_release_workspace() frees it). Pinned host memory copies fastest. */
+int cudadma_seq_copy_host(void *h_dst, const void *h_src, size_t bytes, int chunk_bytes, int impl);
+int cudadma_strided_transpose_host(float *h_dst, const float *h_src, int rows, int cols, int impl);
+int cudadma_gather_scatter_host(void *h_out, size_t out_records, const void *h_table, size_t table_records,
+                                const int32_t *h_gather_idx, const int32_t *h_scatter_idx, size_t n,
+                                int record_bytes, int impl);
+int cudadma_stencil25_run_host(float *h_out, const float *h_in, int nx, int ny, int nz, const float coeff[5],
+                               int steps, int impl);
+int cudadma_release_workspace(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,47 @@
+/*
+ * ref_bench.cu -- the benchmark workloads driven by the REFERENCE CudaDMA
+ * classes (include/cudaDMAv2.h of the CudaDMA project, found through
+ * -I$(REFERENCE_INCLUDE); nothing of it is copied here) compiled for sm_100a.
+ * The kernels are the repository's portable kernels: the same source that the
+ * product library builds against its own header. TEST INFRASTRUCTURE: this is
+ * the "reference CudaDMA build" baseline and a device-side parity oracle.
+ *
+ * Entry points return 0 or a cudaError_t; stream is a cudaStream_t.
+ */
+#include <cuda_runtime.h>
+
+#include "cudaDMAv2.h"
+
+#include "common_kernels.cuh"
+#include "portable_kernels.cuh"
+
+namespace {
+int sm_count() {
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  return n;
+}
+}  // namespace
+
+extern "C" {
+
+int cudadma_ref_seq_copy(void *dst, const void *src, size_t bytes, void *stream) {
+  if (bytes % portable::P_CHUNK) return (int)cudaErrorInvalidValue;
+  return portable::launch_seq_copy(static_cast<char *>(dst), static_cast<const char *>(src),
+                                   (long long)(bytes / portable::P_CHUNK), sm_count(), (cudaStream_t)stream);
+}
+
+int cudadma_ref_strided_transpose(float *dst, const float *src, int rows, int cols, void *stream) {
+  if (rows % portable::PT_ROWS || cols % portable::PT_COLS) return (int)cudaErrorInvalidValue;
+  return portable::launch_transpose(dst, src, rows, cols, sm_count(), (cudaStream_t)stream);
+}
+
+int cudadma_ref_gather_scatter(void *out, const void *table, const int *gather_idx, const int *scatter_idx, size_t n,
+                               void *stream) {
+  if (n % 128) return (int)cudaErrorInvalidValue;
+  return portable::launch_gather_scatter(static_cast<char *>(out), static_cast<const char *>(table), gather_idx,
+                                         scatter_idx, (long long)(n / 128), sm_count(), (cudaStream_t)stream);
+}
+
+} /* extern "C" */

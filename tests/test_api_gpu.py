@@ -1,0 +1,243 @@
+"""Parity of the CudaDMA objects with the oracle, through the single-CTA test
+kernels, over the matrix the reference's tests walk
+(src/tests/test_sequential/cudaDMA_test_sequential_v2.cu:532-617): warp-specialised
+or not x one- or two-phase x plain or qualified x template level, with the
+random parameter distributions of its sweep scripts
+(src/tests/test_strided/param_sweep_v2.py:54-68). Inputs are h_idata[i] = float(i)
+as in the reference tests. All comparisons are bit-exact. Where the reference
+classes compiled for sm_100a are present (oracle/_ref), the same call is run
+through them and the two device results are compared as well.
+"""
+import itertools
+import random
+
+import numpy as np
+import pytest
+
+from oracle import oracle
+from tests import harness
+
+pytestmark = pytest.mark.gpu
+
+MODES = list(itertools.product((1, 0), (0, 1), (0, 1)))  # ws, two_phase, qualified
+OFFSETS = {16: (0,), 8: (0, 2), 4: (0, 1, 2, 3)}
+
+
+def draw_elmt_floats(rng):
+    return max(1, abs(int(np.ceil(rng.gauss(256, 256)))))
+
+
+def expect_sequential(h_in, offset, nbytes):
+    exp = np.zeros_like(h_in)
+    n = nbytes // 4
+    exp[offset:offset + n] = oracle.sequential(h_in[offset:offset + n]).view(np.float32)
+    return exp
+
+
+def check_sequential(level, ws, two_phase, qualified, alignment, offset, nbytes, ndma):
+    buf = nbytes // 4 + offset
+    h_in = np.arange(buf, dtype=np.float32)
+    r, out = harness.ours().sequential(ws, level, two_phase, qualified, alignment, offset, nbytes, ndma, h_in)
+    assert r == 0, "harness status %d" % r
+    exp = expect_sequential(h_in, offset, nbytes)
+    assert np.array_equal(out.view(np.uint32), exp.view(np.uint32))
+    ref = harness.reference_v2()
+    if ref is not None:
+        r2, out2 = ref.sequential(ws, level, two_phase, qualified, alignment, offset, nbytes, ndma, h_in)
+        assert r2 == 0
+        n = nbytes // 4
+        assert np.array_equal(out2[offset:offset + n].view(np.uint32), out[offset:offset + n].view(np.uint32))
+
+
+@pytest.mark.parametrize("ws,two_phase,qualified", MODES)
+def test_sequential_runtime_sized_sweep(ws, two_phase, qualified):
+    rng = random.Random(1000 + 4 * ws + 2 * two_phase + qualified)
+    for _ in range(12):
+        alignment = rng.choice((4, 8, 16))
+        offset = rng.choice(OFFSETS[alignment])
+        floats = min(draw_elmt_floats(rng), 10000)
+        ndma = 32 * rng.randint(1, 16)
+        check_sequential(1, ws, two_phase, qualified, alignment, offset, floats * 4, ndma)
+
+
+@pytest.mark.parametrize("ws,two_phase,qualified", MODES)
+@pytest.mark.parametrize("alignment,nbytes,ndma", [(16, 16384, 128), (8, 1000, 64), (4, 2532, 96)])
+def test_sequential_static_forms(ws, two_phase, qualified, alignment, nbytes, ndma):
+    for level in (2, 3):
+        check_sequential(level, ws, two_phase, qualified, alignment, 0, nbytes, ndma)
+
+
+def test_sequential_edges():
+    # one float, one warp; a 16-byte-aligned body with every possible tail; more threads than data
+    for nbytes in (4, 8, 12, 16, 20, 64, 68, 72, 76, 4096 + 4, 2048 * 3 + 8):
+        for ws in (1, 0):
+            check_sequential(1, ws, 0, 0, 16, 0, nbytes, 32)
+            check_sequential(1, ws, 1, 1, 4, 3, nbytes, 512)
+
+
+def expect_strided(h_in, offset, nbytes, rows, sstride, dpitch, buffer_floats):
+    exp = np.zeros(buffer_floats, dtype=np.float32)
+    oracle.strided(exp[offset:].view(np.uint8), h_in[offset:].view(np.uint8), nbytes, rows, sstride, dpitch)
+    return exp
+
+
+def check_strided(level, ws, two_phase, qualified, alignment, offset, nbytes, rows, sstride, dstride, ndma):
+    dpitch = nbytes if dstride < 0 else dstride
+    in_floats = offset + ((rows - 1) * sstride + nbytes) // 4
+    buffer_floats = offset + ((rows - 1) * dpitch + nbytes) // 4
+    if buffer_floats * 4 > 200 * 1024:
+        return False
+    h_in = np.arange(in_floats, dtype=np.float32)
+    r, out = harness.ours().strided(ws, level, two_phase, qualified, alignment, offset, nbytes, rows, sstride, dstride,
+                                    ndma, h_in, buffer_floats)
+    assert r == 0, "harness status %d" % r
+    exp = expect_strided(h_in, offset, nbytes, rows, sstride, dpitch, buffer_floats)
+    assert np.array_equal(out.view(np.uint32), exp.view(np.uint32))
+    ref = harness.reference_v2()
+    if ref is not None and buffer_floats * 4 <= 48 * 1024:
+        r2, out2 = ref.strided(ws, level, two_phase, qualified, alignment, offset, nbytes, rows, sstride, dstride, ndma,
+                               h_in, buffer_floats)
+        assert r2 == 0
+        # the reference leaves the gaps between rows alone too, so whole buffers must agree
+        assert np.array_equal(out2.view(np.uint32), out.view(np.uint32))
+    return True
+
+
+@pytest.mark.parametrize("ws,two_phase,qualified", MODES)
+def test_strided_runtime_sized_sweep(ws, two_phase, qualified):
+    rng = random.Random(2000 + 4 * ws + 2 * two_phase + qualified)
+    done = 0
+    while done < 10:
+        alignment = rng.choice((4, 8, 16))
+        offset = rng.choice(OFFSETS[alignment])
+        floats = min(draw_elmt_floats(rng), 600)
+        per = alignment // 4
+        min_stride = (floats + per - 1) // per * per  # the reference test's min_stride
+        sstride = (min_stride + per * rng.randint(0, 8)) * 4
+        dstride = rng.choice((-1, min_stride * 4, (min_stride + per * rng.randint(0, 3)) * 4))
+        if dstride == -1 and (floats * 4) % alignment:
+            dstride = min_stride * 4  # packed rows would break the alignment contract
+        rows = rng.randint(1, 32)
+        ndma = 32 * rng.randint(1, 16)
+        done += bool(check_strided(1, ws, two_phase, qualified, alignment, offset, floats * 4, rows, sstride, dstride,
+                                   ndma))
+
+
+@pytest.mark.parametrize("ws,two_phase,qualified", MODES)
+@pytest.mark.parametrize("alignment,nbytes,ndma,rows,sstride,dstride",
+                         [(16, 256, 128, 128, 65536, 256), (16, 256, 128, 128, 1024, 272), (8, 320, 32, 24, 4096, 320),
+                          (4, 100, 64, 7, 132, 104), (4, 100, 64, 7, 100, -1)])
+def test_strided_static_forms(ws, two_phase, qualified, alignment, nbytes, ndma, rows, sstride, dstride):
+    for level in (2, 3, 4):
+        assert check_strided(level, ws, two_phase, qualified, alignment, 0, nbytes, rows, sstride, dstride, ndma)
+
+
+def check_indirect(gather, level, ws, two_phase, qualified, alignment, offset, nbytes, rows, alt, ndma, index):
+    pitch = max(alt, nbytes)
+    buffer_floats = offset + ((rows - 1) * pitch + nbytes) // 4
+    table_floats = offset + (int(max(index)) + 1) * nbytes // 4
+    if buffer_floats * 4 > 200 * 1024:
+        return False
+    h = harness.ours()
+    ref = harness.reference_v2()
+    if gather:
+        h_in = np.arange(table_floats, dtype=np.float32)
+        r, out = h.indirect(1, ws, level, two_phase, qualified, alignment, offset, nbytes, rows, alt, ndma, index, h_in,
+                            buffer_floats, buffer_floats)
+        assert r == 0, "harness status %d" % r
+        exp = np.zeros(buffer_floats, dtype=np.float32)
+        oracle.gather(exp[offset:].view(np.uint8), h_in[offset:].view(np.uint8), index, nbytes, alt)
+        assert np.array_equal(out.view(np.uint32), exp.view(np.uint32))
+        if ref is not None and buffer_floats * 4 <= 48 * 1024:
+            r2, out2 = ref.indirect(1, ws, level, two_phase, qualified, alignment, offset, nbytes, rows, alt, ndma,
+                                    index, h_in, buffer_floats, buffer_floats)
+            assert r2 == 0
+            assert np.array_equal(out2.view(np.uint32), out.view(np.uint32))
+    else:
+        h_in = np.arange(buffer_floats, dtype=np.float32) + 1.0
+        r, out = h.indirect(0, ws, level, two_phase, qualified, alignment, offset, nbytes, rows, alt, ndma, index, h_in,
+                            table_floats, buffer_floats)
+        assert r == 0, "harness status %d" % r
+        exp = np.zeros(table_floats, dtype=np.float32)
+        oracle.scatter(exp[offset:].view(np.uint8), h_in[offset:].view(np.uint8), index, nbytes, alt)
+        assert np.array_equal(out.view(np.uint32), exp.view(np.uint32))
+    return True
+
+
+@pytest.mark.parametrize("gather", (1, 0))
+@pytest.mark.parametrize("ws,two_phase,qualified", MODES)
+def test_indirect_runtime_sized_sweep(gather, ws, two_phase, qualified):
+    rng = random.Random(3000 + 8 * gather + 4 * ws + 2 * two_phase + qualified)
+    done = 0
+    while done < 8:
+        alignment = rng.choice((4, 8, 16))
+        offset = rng.choice(OFFSETS[alignment])
+        per = alignment // 4
+        floats = min(draw_elmt_floats(rng), 400) // per * per  # the sweep requires elmt_size % alignment == 0
+        if floats == 0:
+            continue
+        rows = rng.randint(1, 32)
+        nbytes = floats * 4
+        # the class multiplies the index by the record size (cudaDMAv2.h:13618-13619): distinct record
+        # numbers cannot overlap, which is what the reference test's rejection loop is after
+        index = rng.sample(range(64), rows)
+        alt = rng.choice((0, 0, nbytes + alignment * rng.randint(0, 4)))
+        ndma = 32 * rng.randint(1, 16)
+        done += bool(check_indirect(gather, 1, ws, two_phase, qualified, alignment, offset, nbytes, rows, alt, ndma,
+                                    index))
+
+
+@pytest.mark.parametrize("gather", (1, 0))
+@pytest.mark.parametrize("ws,two_phase,qualified", MODES)
+@pytest.mark.parametrize("alignment,nbytes,ndma,rows", [(16, 32, 128, 128), (8, 40, 32, 9), (4, 12, 64, 20)])
+def test_indirect_static_forms(gather, ws, two_phase, qualified, alignment, nbytes, ndma, rows):
+    rng = random.Random(rows * 7 + nbytes)
+    index = rng.sample(range(4096), rows)
+    for level in (2, 3, 4):
+        for alt in (0, nbytes + 16):
+            assert check_indirect(gather, level, ws, two_phase, qualified, alignment, 0, nbytes, rows, alt, ndma, index)
+
+
+def check_halo(elmt_floats, radius, corners, alignment, offset, dimx, dimy, pitch, ndma, rng):
+    in_elems = pitch * (dimy + 2 * radius) + offset
+    h_in = np.array([rng.randrange(10) for _ in range(in_elems * elmt_floats)], dtype=np.float32) + 1.0
+    r, out = harness.ours().halo(elmt_floats, radius, corners, alignment, offset, dimx, dimy, pitch, ndma, h_in)
+    assert r == 0, "harness status %d" % r
+    exp = np.zeros_like(out)
+    eb = 4 * elmt_floats
+    oracle.halo_ring(exp[offset * elmt_floats:].view(np.uint8), h_in[offset * elmt_floats:].view(np.uint8), dimx, dimy,
+                     pitch, radius, corners, eb)
+    # the ring is copied and nothing else is touched (interior and, without corners, the corner blocks stay zero)
+    assert np.array_equal(out.view(np.uint32), exp.view(np.uint32))
+    ref = harness.reference_v1()
+    # the reference's own halo test only enables ALIGNMENT 4 (cudaDMA_test_halo.cu:388-394): stay inside it
+    if ref is not None and alignment == 4 and out.nbytes <= 48 * 1024:
+        r2, out2 = ref.halo(elmt_floats, radius, corners, alignment, offset, dimx, dimy, pitch, ndma, h_in)
+        assert r2 == 0
+        ring = exp != 0  # inputs are >= 1, so the ring is exactly where the expectation is non-zero
+        assert np.array_equal(out2[ring].view(np.uint32), out[ring].view(np.uint32))
+
+
+@pytest.mark.parametrize("corners", (0, 1))
+@pytest.mark.parametrize("radius", (1, 2, 4, 8))
+def test_halo_sweep(radius, corners):
+    """The nested sweep of src/tests/test_halo/cudaDMA_test_halo.cu:298-373, sampled."""
+    rng = random.Random(4000 + 10 * radius + corners)
+    for elmt_floats in (1, 2, 4):
+        for _ in range(6):
+            alignment = rng.choice((4, 8, 16))
+            per = max(1, alignment // (4 * elmt_floats))
+            dimx = rng.randrange(8, 64) // per * per or per
+            dimy = rng.randrange(8, 64)
+            pitch = rng.choice((dimx + 2 * radius, 4 * dimx, (dimx + 2 * radius + 3) // 4 * 4 + 4))
+            pitch = max(pitch, dimx + 2 * radius)
+            offset = 0 if alignment > 4 * elmt_floats else rng.randrange(4)
+            ndma = 32 * rng.randint(1, 16)
+            check_halo(elmt_floats, radius, corners, alignment, offset, dimx, dimy, pitch, ndma, rng)
+
+
+def test_halo_benchmark_shape():
+    # the 32 x 16 tile, radius 4, of the stencil configuration
+    rng = random.Random(5)
+    check_halo(1, 4, 0, 16, 0, 32, 16, 512, 128, rng)
+    check_halo(1, 4, 1, 16, 0, 32, 16, 512, 32, rng)

@@ -1,0 +1,207 @@
+"""Parity of the four single-GPU workloads, called through the C ABI, with the
+CPU oracle: bit-exact for copy, transpose and gather/scatter; within 1e-5
+(max |gpu - ref| / max |ref|) of the double-precision oracle for the stencil.
+Small cases are compared element by element; the full benchmark sizes are
+checked through properties that do not need the oracle to walk them twice.
+"""
+import numpy as np
+import pytest
+import torch
+
+import cudadma_b200 as cd
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+IMPLS = ("native", "portable")
+STENCIL_TOL = 1e-5  # L-infinity relative, the tolerance the benchmark states
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def status_clean():
+    assert cd.device_status() == 0
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+@pytest.mark.parametrize("nbytes,chunk", [(16384, 16384), (16384 * 37, 16384), (16384 * 300 + 4096 + 8, 16384),
+                                          (4, 16384), (1 << 20, 4096), (100000, 1008)])
+def test_seq_copy_small(impl, nbytes, chunk):
+    src = oracle.fill_uniform(nbytes // 4, 0xC1, -1.0, 1.0)
+    d_src = dev(src)
+    d_dst = torch.zeros(nbytes // 4 + 64, dtype=torch.float32, device="cuda")
+    cd.seq_copy(d_dst, d_src, nbytes, chunk, impl)
+    status_clean()
+    out = d_dst.cpu().numpy()
+    exp = oracle.chunked_copy(src, chunk)
+    assert np.array_equal(out[:nbytes // 4].view(np.uint32), exp.view(np.uint32))
+    assert not out[nbytes // 4:].any(), "wrote past the end"
+
+
+def test_seq_copy_rejects_bad_arguments():
+    t = torch.zeros(1024, dtype=torch.float32, device="cuda")
+    for args in ((t, t, 6, 16384), (t, t, 64, 100), (t, t, 64, 32768)):
+        with pytest.raises(cd.CudaDMAError) as e:
+            cd.seq_copy(*args)
+        assert e.value.status == -1
+    # misaligned pointer, null pointer, overlapping stencil buffers
+    assert cd.lib().cudadma_seq_copy(t.data_ptr() + 4, t.data_ptr(), 64, 16384, 0, None) == -1
+    assert cd.lib().cudadma_seq_copy(None, t.data_ptr(), 64, 16384, 0, None) == -1
+    with pytest.raises(cd.CudaDMAError):
+        cd.stencil25_step(t, t, 16, 8, 8)
+    with pytest.raises(cd.CudaDMAError):
+        cd.gather_scatter(t, t, t, t, 100, 32)
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_seq_copy_full_size(impl):
+    """64 MiB, 16 KiB chunks: the benchmark's configuration, compared on the device with the source."""
+    n = 1 << 24
+    d_src = dev(oracle.fill_uniform(n, 0xC1, -1.0, 1.0))
+    d_dst = torch.zeros_like(d_src)
+    cd.seq_copy(d_dst, d_src, n * 4, 16384, impl)
+    status_clean()
+    assert torch.equal(d_dst.view(torch.int32), d_src.view(torch.int32))
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+@pytest.mark.parametrize("rows,cols", [(128, 64), (256, 192), (1024, 2048), (128 * 7, 64 * 37)])
+def test_transpose_small(impl, rows, cols):
+    src = oracle.fill_uniform(rows * cols, 0xC2, -1.0, 1.0).reshape(rows, cols)
+    d_src = dev(src)
+    d_dst = torch.zeros(cols * rows + 64, dtype=torch.float32, device="cuda")
+    cd.strided_transpose(d_dst, d_src, rows, cols, impl)
+    status_clean()
+    out = d_dst.cpu().numpy()
+    exp = oracle.tile_transpose(src)
+    assert np.array_equal(out[:rows * cols].view(np.uint32), exp.ravel().view(np.uint32))
+    assert not out[rows * cols:].any()
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_transpose_full_size_is_an_involution(impl):
+    """16384 x 16384: transposing twice gives the input back, and one transpose matches torch's."""
+    n = 16384
+    d_src = torch.empty(n * n, dtype=torch.float32, device="cuda")
+    # seeded fill made on the device in pieces to keep host memory small
+    piece = 1 << 26
+    for i in range(0, n * n, piece):
+        d_src[i:i + piece] = dev(oracle.fill_uniform(piece, 0xC2 + i, -1.0, 1.0))
+    d_t = torch.empty_like(d_src)
+    cd.strided_transpose(d_t, d_src, n, n, impl)
+    status_clean()
+    assert torch.equal(d_t.view(n, n), d_src.view(n, n).t())
+    d_back = torch.empty_like(d_src)
+    cd.strided_transpose(d_back, d_t, n, n, impl)
+    assert torch.equal(d_back, d_src)
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+@pytest.mark.parametrize("n,table_records", [(128, 1000), (128 * 5, 128 * 5), (128 * 333, 1 << 16), (1 << 16, 1 << 20)])
+def test_gather_scatter_small(impl, n, table_records):
+    table = oracle.fill_uniform(table_records * 8, 0xC3, -1.0, 1.0)
+    gidx = oracle.fill_index(n, 0xC3A, table_records)
+    sidx = oracle.permutation(n, 0xC3B)
+    d_out = torch.zeros(n * 8 + 64, dtype=torch.float32, device="cuda")
+    cd.gather_scatter(d_out, dev(table), dev(gidx), dev(sidx), n, 32, impl)
+    status_clean()
+    out = d_out.cpu().numpy()
+    exp = oracle.gather_scatter(np.zeros(n * 8, dtype=np.float32), table, gidx, sidx, 32)
+    assert np.array_equal(out[:n * 8].view(np.uint32), exp.view(np.uint32))
+    assert not out[n * 8:].any()
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_gather_scatter_full_size(impl):
+    """2^24-record table, 2^22 indices: every output slot holds the record its index names
+    (checked on the device through the inverse permutation)."""
+    n, records = 1 << 22, 1 << 24
+    d_table = torch.empty(records * 8, dtype=torch.float32, device="cuda")
+    piece = 1 << 25
+    for i in range(0, records * 8, piece):
+        d_table[i:i + piece] = dev(oracle.fill_uniform(piece, 0xC3 + i, -1.0, 1.0))
+    d_g = dev(oracle.fill_index(n, 0xC3A, records))
+    d_s = dev(oracle.permutation(n, 0xC3B))
+    d_out = torch.zeros(n * 8, dtype=torch.float32, device="cuda")
+    cd.gather_scatter(d_out, d_table, d_g, d_s, n, 32, impl)
+    status_clean()
+    exp = torch.empty(n, 8, dtype=torch.float32, device="cuda")
+    exp[d_s.long()] = d_table.view(records, 8)[d_g.long()]
+    assert torch.equal(d_out.view(n, 8).view(torch.int32), exp.view(torch.int32))
+
+
+def rel_err(a, b):
+    return float(np.abs(a.astype(np.float64) - b.astype(np.float64)).max() / np.abs(b).max())
+
+
+@pytest.mark.parametrize("nx,ny,nz,steps", [(32, 16, 8, 1), (64, 48, 40, 3), (96, 80, 33, 2), (36, 20, 19, 2),
+                                            (128, 64, 72, 10)])
+def test_stencil_small(nx, ny, nz, steps):
+    field = oracle.fill_uniform(nx * ny * nz, 0xC4, 0.0, 1.0).reshape(nz, ny, nx)
+    a = dev(field)
+    b = torch.zeros_like(a)
+    res = cd.stencil25_run(a, b, nx, ny, nz, steps)
+    status_clean()
+    exp = oracle.stencil25_f64(field, cd.STENCIL_COEFFS, steps)
+    assert rel_err(res.cpu().numpy(), exp) <= STENCIL_TOL
+
+
+def test_stencil_plane_ranges_compose():
+    """Computing [0, k) and [k, nz) separately equals one full step bit for bit (what the sharded driver relies on)."""
+    nx, ny, nz = 64, 32, 50
+    a = dev(oracle.fill_uniform(nx * ny * nz, 0xC4, 0.0, 1.0))
+    full = torch.zeros_like(a)
+    cd.stencil25_step(full, a, nx, ny, nz)
+    parts = torch.zeros_like(a)
+    cd.stencil25_step(parts, a, nx, ny, nz, 0, 4)
+    cd.stencil25_step(parts, a, nx, ny, nz, 4, 46, z_chunk=7)
+    cd.stencil25_step(parts, a, nx, ny, nz, 46, 50)
+    status_clean()
+    assert torch.equal(full.view(torch.int32), parts.view(torch.int32))
+
+
+def test_stencil_full_size_linearity_and_sample():
+    """512^3, 10 steps. The operator is linear: stepping 2u equals twice stepping u exactly (scaling by two is exact
+    in fp32), and a slab of the one-step result is compared with the double-precision oracle."""
+    n = 512
+    field = oracle.fill_uniform(n * n * n, 0xC4, 0.0, 1.0)
+    a = dev(field)
+    b = torch.zeros_like(a)
+    a2 = a * 2.0
+    b2 = torch.zeros_like(a)
+    r1 = cd.stencil25_run(a, b, n, n, n, 10)
+    r2 = cd.stencil25_run(a2, b2, n, n, n, 10)
+    status_clean()
+    assert torch.equal((r1 * 2.0).view(torch.int32), r2.view(torch.int32))
+    del a2, b2, r2
+    # one step on a 24-plane slab at the top of the grid against the oracle (out-of-grid planes read as zero)
+    slab = field.reshape(n, n, n)[:28]
+    exp = oracle.stencil25_f64(np.ascontiguousarray(slab), cd.STENCIL_COEFFS, 1)[:24]
+    a = dev(field)
+    cd.stencil25_step(b, a, n, n, n, 0, 24)
+    got = b.view(n, n, n)[:24].cpu().numpy()
+    assert rel_err(got, exp) <= STENCIL_TOL
+
+
+def test_host_buffer_forms_match_device_forms():
+    n = 16384 * 9
+    src = oracle.fill_uniform(n // 4, 0xC1, -1.0, 1.0)
+    out = np.zeros_like(src)
+    cd.seq_copy_host(out, src, n)
+    assert np.array_equal(out.view(np.uint32), src.view(np.uint32))
+    m = oracle.fill_uniform(256 * 128, 0xC2, -1.0, 1.0).reshape(256, 128)
+    t = np.zeros((128, 256), dtype=np.float32)
+    cd.strided_transpose_host(t, m, 256, 128)
+    assert np.array_equal(t, m.T)
+    table = oracle.fill_uniform(4096 * 8, 0xC3, -1.0, 1.0)
+    g = oracle.fill_index(1280, 0xC3A, 4096)
+    s = oracle.permutation(1280, 0xC3B)
+    o = np.zeros(1280 * 8, dtype=np.float32)
+    cd.gather_scatter_host(o, 1280, table, 4096, g, s, 1280)
+    assert np.array_equal(o, oracle.gather_scatter(np.zeros_like(o), table, g, s))
+    f = oracle.fill_uniform(64 * 32 * 20, 0xC4, 0.0, 1.0).reshape(20, 32, 64)
+    r = np.zeros_like(f)
+    cd.stencil25_run_host(r, f, 64, 32, 20, 3)
+    assert rel_err(r, oracle.stencil25_f64(f, cd.STENCIL_COEFFS, 3)) <= STENCIL_TOL
+    cd.release_workspace()
