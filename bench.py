@@ -1,0 +1,525 @@
+"""Benchmark of the hot path: the radius-4 25-point stencil fed by CudaDMA objects,
+on the sharded configuration of the benchmark list (1024 x 1024 x 2048 fp32 grid,
+z-split over the ranks, four-plane halos exchanged every step), plus, at one GPU,
+the three data-movement patterns and the 512^3 stencil.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One process per GPU (torchrun sets RANK / LOCAL_RANK / WORLD_SIZE for N > 1). A
+step is one time step over the whole grid. Rank 0 prints one JSON line.
+
+--impl ours       this repository's kernels.
+--impl reference  the same workloads through the REFERENCE CudaDMA classes compiled for
+                  sm_100a (oracle/_ref, built from the reference checkout) where that
+                  library is present, else the CPU restatement on the host cores.
+Both lines carry `cpu_baseline`: the host loops of oracle/ on a bounded sample.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch
+import torch.distributed as dist
+
+NX, NY, NZ = 1024, 1024, 2048          # the sharded stencil configuration
+C4 = (512, 512, 512)                   # the single-GPU stencil configuration
+BYTES_PER_POINT = 8                    # one fp32 read + one fp32 write per point and step
+L2_FLUSH_BYTES = 256 << 20
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for l in self.lines:
+            parts = [x.strip() for x in l.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def setup_dist(n_gpus):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if world != n_gpus and rank == 0:
+        print("warning: --gpus %d but WORLD_SIZE=%d; using WORLD_SIZE" % (n_gpus, world), file=sys.stderr)
+    return rank, world, local
+
+
+def barrier():
+    if dist.is_initialized():
+        dist.barrier()
+
+
+def max_over_ranks(x):
+    if not dist.is_initialized():
+        return x
+    t = torch.tensor([x], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def time_region(fn, reps):
+    """Device time of `reps` calls of fn, in ms, bracketed by barrier + synchronize; max over ranks."""
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    barrier()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    barrier()
+    return max_over_ranks(e0.elapsed_time(e1))
+
+
+def median_launch_ms(fn, reps, flush=None):
+    """Median device time of single calls, each timed by its own event pair (L2 flushed before each if asked)."""
+    ts = []
+    for _ in range(reps):
+        if flush is not None:
+            flush.add_(1.0)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        e1.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2], ts[0]
+
+
+def seeded_field(n, seed):
+    g = torch.Generator(device="cuda")
+    g.manual_seed(seed)
+    return torch.rand(n, generator=g, device="cuda", dtype=torch.float32)
+
+
+# ------------------------------------------------------------------ CPU baseline
+def cpu_baseline_stencil():
+    """The oracle's fp32 stencil step (oracle/oracle.c, all host threads) on a 1024 x 1024 x 64 slab."""
+    import numpy as np
+    from oracle import oracle
+    nz = 64
+    field = oracle.fill_uniform(NX * NY * nz, 0xC4, 0.0, 1.0).reshape(nz, NY, NX)
+    out = np.empty_like(field)
+    coeff = (-2.847, 1.6, -0.2, 0.0254, -0.00179)
+    oracle.stencil25_step_f32(field, coeff, out)  # warm-up
+    reps, t0 = 0, time.perf_counter()
+    while reps < 3 or time.perf_counter() - t0 < 5.0:
+        oracle.stencil25_step_f32(field, coeff, out)
+        reps += 1
+    dt = time.perf_counter() - t0
+    return {"value": NX * NY * nz * reps / dt / 1e9, "unit": "Gpts/s", "cores": oracle.num_threads(), "kind": "port",
+            "sample": "%d steps of the fp32 host loop on a %dx%dx%d slab of the grid" % (reps, NX, NY, nz)}
+
+
+def cpu_baseline_patterns():
+    import numpy as np
+    from oracle import oracle
+    out = {}
+
+    def rate(fn, nbytes):
+        fn()
+        reps, t0 = 0, time.perf_counter()
+        while reps < 2 or time.perf_counter() - t0 < 2.0:
+            fn()
+            reps += 1
+        return nbytes * reps / (time.perf_counter() - t0) / 1e9
+
+    src = oracle.fill_uniform(1 << 24, 0xC1, -1.0, 1.0)
+    out["sequential_gbs"] = rate(lambda: oracle.chunked_copy(src), 2 * src.nbytes)
+    m = oracle.fill_uniform(4096 * 4096, 0xC2, -1.0, 1.0).reshape(4096, 4096)
+    t = np.empty((4096, 4096), dtype=np.float32)
+    out["strided_gbs"] = rate(lambda: oracle.tile_transpose(m, out=t), 2 * m.nbytes)
+    out["strided_sample"] = "4096x4096 of the 16384x16384 matrix"
+    n, rec = 1 << 22, 1 << 24
+    table = oracle.fill_uniform(rec * 8, 0xC3, -1.0, 1.0)
+    g, s = oracle.fill_index(n, 0xC3A, rec), oracle.permutation(n, 0xC3B)
+    o = np.zeros(n * 8, dtype=np.float32)
+    out["indirect_gbs"] = rate(lambda: oracle.gather_scatter(o, table, g, s), n * 72)
+    out["cores"] = oracle.num_threads()
+    return out
+
+
+# ------------------------------------------------------------------ single-GPU patterns
+def run_patterns(kind, peak):
+    """Device-timed GB/s of the three data-movement patterns and the 512^3 stencil.
+    kind: "native", "portable" (this repository) or "reference" (oracle/_ref)."""
+    import cudadma_b200 as cd
+    if kind == "reference":
+        from oracle import reference as ref
+    flush = torch.zeros(L2_FLUSH_BYTES // 4, device="cuda")
+    res = {}
+
+    def entry(ms, best, nbytes, launches=1):
+        gbs = nbytes / ms / 1e6
+        return {"gbs": round(gbs, 1), "frac_of_peak": round(gbs / peak, 4), "ms": round(ms, 4),
+                "best_gbs": round(nbytes / best / 1e6, 1), "algorithmic_bytes": nbytes, "launches_per_pass": launches}
+
+    # sequential: 64 MiB, 16 KiB chunks
+    n = 1 << 24
+    src, dst = seeded_field(n, 0xC1) * 2 - 1, torch.empty(n, device="cuda")
+    if kind == "reference":
+        f = lambda: ref.seq_copy(dst, src, n * 4)
+    else:
+        f = lambda: cd.seq_copy(dst, src, n * 4, 16384, kind)
+    for _ in range(3):
+        f()
+    ms, best = median_launch_ms(f, 30, flush)
+    res["sequential_64MiB"] = entry(ms, best, 2 * n * 4)
+    # the same kernel on 1 GiB, where launch and tail effects no longer dominate
+    nb = 1 << 28
+    big_s, big_d = seeded_field(nb, 0xC1), torch.empty(nb, device="cuda")
+    if kind == "reference":
+        f = lambda: ref.seq_copy(big_d, big_s, nb * 4)
+    else:
+        f = lambda: cd.seq_copy(big_d, big_s, nb * 4, 16384, kind)
+    for _ in range(3):
+        f()
+    ms, best = median_launch_ms(f, 10)
+    res["sequential_1GiB"] = entry(ms, best, 2 * nb * 4)
+    ok = torch.equal(big_d.view(torch.int32), big_s.view(torch.int32))
+    res["sequential_1GiB"]["parity"] = "pass" if ok else "FAIL"
+    del big_s, big_d, src, dst
+
+    # strided: 16384 x 16384 transpose in 128 x 64 tiles (1 GiB in, 1 GiB out: larger than L2)
+    m = 16384
+    a, b = seeded_field(m * m, 0xC2) * 2 - 1, torch.empty(m * m, device="cuda")
+    if kind == "reference":
+        f = lambda: ref.strided_transpose(b, a, m, m)
+    else:
+        f = lambda: cd.strided_transpose(b, a, m, m, kind)
+    for _ in range(3):
+        f()
+    ms, best = median_launch_ms(f, 10)
+    res["strided_16384"] = entry(ms, best, 2 * m * m * 4)
+    res["strided_16384"]["parity"] = "pass" if torch.equal(b.view(m, m)[:512], a.view(m, m).t()[:512]) else "FAIL"
+    del a, b
+
+    # indirect: 2^24 x 32 B table, 2^22 gathers, scattered through a permutation
+    n, rec = 1 << 22, 1 << 24
+    g = torch.Generator(device="cuda")
+    g.manual_seed(0xC3A)
+    table = seeded_field(rec * 8, 0xC3)
+    gi = torch.randint(0, rec, (n,), generator=g, device="cuda", dtype=torch.int32)
+    si = torch.randperm(n, generator=g, device="cuda").to(torch.int32)
+    out = torch.zeros(n * 8, device="cuda")
+    if kind == "reference":
+        f = lambda: ref.gather_scatter(out, table, gi, si, n)
+    else:
+        f = lambda: cd.gather_scatter(out, table, gi, si, n, 32, kind)
+    for _ in range(3):
+        f()
+    ms, best = median_launch_ms(f, 20, flush)
+    res["indirect_2e22x32B"] = entry(ms, best, n * 72)
+    res["indirect_2e22x32B"]["payload_gbs"] = round(n * 64 / ms / 1e6, 1)
+    exp = torch.empty(n, 8, device="cuda")
+    exp[si.long()] = table.view(rec, 8)[gi.long()]
+    res["indirect_2e22x32B"]["parity"] = "pass" if torch.equal(out.view(n, 8), exp) else "FAIL"
+    del table, out, exp
+
+    # stencil 512^3, 10 steps
+    nx, ny, nz = C4
+    pts = nx * ny * nz
+    if kind == "native":
+        a, b = seeded_field(pts, 0xC4), torch.zeros(pts, device="cuda")
+        f = lambda: cd.stencil25_run(a, b, nx, ny, nz, 10, None, kind)
+    else:
+        pad = (nx + 8) * (ny + 8) * (nz + 8)
+        a, b = torch.zeros(pad, device="cuda"), torch.zeros(pad, device="cuda")
+        a.view(nz + 8, ny + 8, nx + 8)[4:-4, 4:-4, 4:-4] = seeded_field(pts, 0xC4).view(nz, ny, nx)
+        step = ref.stencil25_step_padded if kind == "reference" else cd.stencil25_step_padded
+        coeff = cd.STENCIL_COEFFS
+
+        def f():
+            x, y = a, b
+            for _ in range(10):
+                step(y, x, nx, ny, nz, 0, nz, coeff)
+                x, y = y, x
+    f()
+    ms, best = median_launch_ms(f, 5)
+    res["stencil_512"] = entry(ms / 10, best / 10, pts * BYTES_PER_POINT)
+    res["stencil_512"]["gpts"] = round(pts * 10 / ms / 1e6, 1)
+    del a, b
+    if kind != "reference":
+        res["device_status"] = cd.device_status()
+    return res
+
+
+# ------------------------------------------------------------------ the stencil job
+def make_stencil(impl, nz_global):
+    """The sharded stencil driver with this arm's step function."""
+    import cudadma_b200 as cd
+    from cudadma_b200.sharded import ShardedStencil
+    if impl == "ours":
+        return ShardedStencil(NX, NY, nz_global)
+    from oracle import reference as ref
+
+    def step(out, inp, nx, ny, nz_total, zb, ze, coeff):
+        # padded layout: the four ghost planes of a slab are the z border of the padded array
+        ref.stencil25_step_padded(out, inp, nx, ny, nz_total - 8, zb - 4, ze - 4, coeff)
+    return ShardedStencil(NX, NY, nz_global, step_fn=step, pad_xy=4, device=torch.device("cuda", torch.cuda.current_device()))
+
+
+def run_stencil_job(impl, args, rank, world, local, peak, peak_kind):
+    import cudadma_b200 as cd
+    st = make_stencil(impl, NZ)
+    slab_pts = NX * NY * st.nzl
+    st.load(seeded_field(slab_pts, 0xC4 + rank))
+    for _ in range(max(args.warmup, 3)):
+        st.step()
+    with ClockSampler(local) as clocks:
+        ms = time_region(st.step, args.steps)
+        if ms < 400.0:  # give the sampler a few periods: repeat the same region, untimed for the record
+            reps = int(400.0 / max(ms, 1e-3))
+            for _ in range(reps):
+                for _ in range(args.steps):
+                    st.step()
+            torch.cuda.synchronize()
+    pts = NX * NY * NZ
+    value = pts * args.steps / ms / 1e6  # Gpts/s, whole job
+    per_step_ms = ms / args.steps
+    status = cd.device_status() if impl == "ours" else 0
+
+    # weak-scaling companion: 256 planes per GPU (the 8-GPU point is the configuration above)
+    weak = None
+    if not args.no_weak:
+        del st
+        torch.cuda.empty_cache()
+        stw = make_stencil(impl, 256 * world)
+        stw.load(seeded_field(NX * NY * stw.nzl, 0xC4 + rank))
+        for _ in range(3):
+            stw.step()
+        msw = time_region(stw.step, args.steps)
+        weak = {"grid": [NX, NY, 256 * world], "value": round(NX * NY * 256 * world * args.steps / msw / 1e6, 2),
+                "unit": "Gpts/s", "ms_per_step": round(msw / args.steps, 4)}
+        del stw
+        torch.cuda.empty_cache()
+        st = make_stencil(impl, NZ)
+
+    # end to end: pinned host slab -> device, K steps with halo exchange, device -> pinned host slab
+    h_in = torch.empty(slab_pts, dtype=torch.float32).pin_memory()
+    h_out = torch.empty(slab_pts, dtype=torch.float32).pin_memory()
+    h_in.uniform_(0.0, 1.0)
+    st.run_host(h_out, h_in, 1)  # warm-up (also faults the pinned pages in)
+    torch.cuda.synchronize()
+    barrier()
+    t0 = time.perf_counter()
+    st.run_host(h_out, h_in, args.steps)
+    torch.cuda.synchronize()
+    barrier()
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    e2e = {"value": round(pts * args.steps / e2e_s / 1e9, 3), "unit": "Gpts/s",
+           "h2d_bytes_per_step": slab_pts * 4 // args.steps, "d2h_bytes_per_step": slab_pts * 4 // args.steps,
+           "note": "whole job through ShardedStencil.run_host: the slab is uploaded once, stepped %d times and "
+                   "downloaded once; bytes are per rank, divided by the steps" % args.steps,
+           "seconds": round(e2e_s, 4)}
+    del h_in, h_out
+
+    line = {
+        "metric": "stencil Gpts/s (radius-4 25-point fp32, %dx%dx%d z-sharded over N GPUs)" % (NX, NY, NZ),
+        "value": round(value, 2), "unit": "Gpts/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": round(per_step_ms, 4), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "sharded 25-point stencil, grid %dx%dx%d, 32x16 tiles + radius-4 halo, "
+                               "4-plane halo exchange per step" % (NX, NY, NZ),
+                   "planes_per_gpu": NZ // world, "exchange": "torch.distributed send/recv (NCCL)" if world > 1 else "none",
+                   "l2": "inputs larger than L2 (%.1f GiB per array per GPU)" % (slab_pts * 4 / 2**30),
+                   "synthetic_for": "uniform[0,1) field from a seeded generator"},
+        "roofline": {"bound": "hbm", "achieved": round(BYTES_PER_POINT * pts / world / per_step_ms / 1e6, 1),
+                     "peak": peak, "unit": "GB/s",
+                     "frac": round(BYTES_PER_POINT * pts / world / per_step_ms / 1e6 / peak, 4), "traffic": None,
+                     "peak_kind": "of " + peak_kind,
+                     "kernel": "stencil25::tensor_kernel" if impl == "ours" else "portable::stencil_kernel",
+                     "algorithmic_bytes_per_launch": BYTES_PER_POINT * pts // world},
+        "e2e": e2e, "clocks": clocks.summary(), "device_status": status,
+    }
+    if weak is not None:
+        line["weak"] = weak
+    return line, st
+
+
+def profile_case(case, reps):
+    """A small, fixed case of one kernel for a profiler capture: few launches, no timing, no JSON.
+    Sizes exceed the L2 (so DRAM counters mean something) and stay near 1 GiB on the device."""
+    import cudadma_b200 as cd
+    torch.cuda.set_device(0)
+    if case == "stencil_512":
+        nx, ny, nz = C4
+        a, b = seeded_field(nx * ny * nz, 0xC4), torch.zeros(nx * ny * nz, device="cuda")
+        for _ in range(reps):
+            cd.stencil25_step(b, a, nx, ny, nz)
+            a, b = b, a
+    elif case == "sequential":
+        n = 1 << 27  # 512 MiB in, 512 MiB out
+        a, b = seeded_field(n, 0xC1), torch.empty(n, device="cuda")
+        for _ in range(reps):
+            cd.seq_copy(b, a, n * 4)
+    elif case == "strided":
+        m = 8192     # 256 MiB in, 256 MiB out
+        a, b = seeded_field(m * m, 0xC2), torch.empty(m * m, device="cuda")
+        for _ in range(reps):
+            cd.strided_transpose(b, a, m, m)
+    elif case == "indirect":
+        n, rec = 1 << 22, 1 << 24
+        g = torch.Generator(device="cuda")
+        g.manual_seed(0xC3A)
+        table = seeded_field(rec * 8, 0xC3)
+        gi = torch.randint(0, rec, (n,), generator=g, device="cuda", dtype=torch.int32)
+        si = torch.randperm(n, generator=g, device="cuda").to(torch.int32)
+        out = torch.zeros(n * 8, device="cuda")
+        for _ in range(reps):
+            cd.gather_scatter(out, table, gi, si, n)
+    else:
+        raise SystemExit("unknown case " + case)
+    torch.cuda.synchronize()
+    if cd.device_status() != 0:
+        raise SystemExit("a wait inside a kernel gave up")
+    print("profile case %s: %d launches done" % (case, reps))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--no-patterns", action="store_true", help="skip the single-GPU data-movement patterns")
+    ap.add_argument("--no-weak", action="store_true", help="skip the weak-scaling companion run")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
+    ap.add_argument("--profile-case", default=None,
+                    help="run only a small case of one kernel (stencil_512, sequential, strided, indirect) "
+                         "--steps times, for a profiler capture")
+    args = ap.parse_args()
+    peak, peak_kind = measured_peaks()
+    if args.profile_case:
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device")
+        profile_case(args.profile_case, args.steps)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    rank, world, local = setup_dist(args.gpus)
+
+    impl = args.impl
+    ref_gpu = False
+    if impl == "reference":
+        from oracle import reference as ref
+        ref_gpu = ref.available() and hasattr(ref.lib(), "cudadma_ref_stencil25_step_padded")
+        if not ref_gpu:
+            # the reference's classes were not compiled here: time the CPU restatement, rank 0 only
+            if rank == 0:
+                cb = cpu_baseline_stencil()
+                print(json.dumps({
+                    "impl": "reference", "metric": "stencil Gpts/s (radius-4 25-point fp32, %dx%dx%d)" % (NX, NY, NZ),
+                    "value": round(cb["value"], 4), "unit": "Gpts/s", "n_gpus": world, "steps": args.steps,
+                    "warmup": args.warmup, "ms_per_step": round(NX * NY * NZ / cb["value"] / 1e6, 2),
+                    "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+                    "data": "synthetic", "config": {"workload": "CPU restatement, " + cb["sample"]},
+                    "cpu_baseline": cb,
+                    "e2e": {"value": round(cb["value"], 4), "unit": "Gpts/s", "h2d_bytes_per_step": 0,
+                            "d2h_bytes_per_step": 0}}))
+            if dist.is_initialized():
+                dist.destroy_process_group()
+            return
+
+    import cudadma_b200 as cd
+    before = cd.launch_count()
+    line, st = run_stencil_job(impl, args, rank, world, local, peak, peak_kind)
+    del st
+    torch.cuda.empty_cache()
+    if impl == "ours":
+        # launches of this library per timed step: one kernel at N = 1, three (two boundary runs + interior) at N > 1
+        line["gpu_launches"] = args.steps * (1 if world == 1 else 3)
+        line["launches_total_this_process"] = cd.launch_count() - before
+    else:
+        line["impl"] = "reference"
+        line["config"]["reference_build"] = ("reference CudaDMA classes (cudaDMAv2.h) compiled for sm_100a, "
+                                             "CudaDMAStrided window loads from zero-padded arrays")
+    if rank == 0 and world == 1 and not args.no_patterns:
+        if impl == "ours":
+            line["patterns"] = {"native": run_patterns("native", peak), "portable": run_patterns("portable", peak)}
+        else:
+            line["patterns"] = {"reference": run_patterns("reference", peak)}
+    if rank == 0 and not args.no_cpu and (world == 1 or impl == "reference"):
+        line["cpu_baseline"] = cpu_baseline_stencil()
+        if world == 1:
+            line["cpu_baseline"]["patterns"] = cpu_baseline_patterns()
+    if rank == 0:
+        print(json.dumps(line))
+    if dist.is_initialized():
+        barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

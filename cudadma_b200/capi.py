@@ -35,6 +35,9 @@ SYMBOLS = [
     ("cudadma_stencil25_run", _c.c_int,
      [_c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.POINTER(_c.c_float), _c.c_int, _c.c_int,
       _c.c_void_p]),
+    ("cudadma_stencil25_step_padded", _c.c_int,
+     [_c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.POINTER(_c.c_float), _c.c_int,
+      _c.c_int, _c.c_void_p]),
     ("cudadma_seq_copy_host", _c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_int, _c.c_int]),
     ("cudadma_strided_transpose_host", _c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int]),
     ("cudadma_gather_scatter_host", _c.c_int,
@@ -163,6 +166,17 @@ def stencil25_step(out, inp, nx, ny, nz, z_begin=0, z_end=None, coeff=None, z_ch
     _check("cudadma_stencil25_step",
            lib().cudadma_stencil25_step(_ptr(out), _ptr(inp), nx, ny, nz, z_begin, z_end, _coeffs(coeff), z_chunk,
                                         _IMPLS[impl], _stream(stream)))
+
+
+def stencil25_step_padded(out, inp, nx, ny, nz, z_begin=0, z_end=None, coeff=None, z_chunk=0, impl="portable",
+                          stream=None):
+    """One step on arrays padded by four zero cells on every side (portable kernels only)."""
+    _require_cuda(out, inp)
+    if z_end is None:
+        z_end = nz
+    _check("cudadma_stencil25_step_padded",
+           lib().cudadma_stencil25_step_padded(_ptr(out), _ptr(inp), nx, ny, nz, z_begin, z_end, _coeffs(coeff),
+                                               z_chunk, _IMPLS[impl], _stream(stream)))
 
 
 def stencil25_run(a, b, nx, ny, nz, steps, coeff=None, impl="native", stream=None):

@@ -9,6 +9,8 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <string.h>
+
 #include <atomic>
 #include <mutex>
 
@@ -93,7 +95,7 @@ int allow_smem(K kernel, int bytes) {
 }
 
 /* ---- grow-only device workspace for the host-buffer forms ---- */
-std::mutex g_ws_mutex;
+std::recursive_mutex g_ws_mutex;
 void *g_ws[4] = {nullptr, nullptr, nullptr, nullptr};
 size_t g_ws_bytes[4] = {0, 0, 0, 0};
 cudaStream_t g_ws_stream = nullptr;
@@ -119,6 +121,47 @@ int finish_status(cudaStream_t s) {
   unsigned int w = 0;
   CK(cudadma_b200::read_status(&w, s));
   return w ? CUDADMA_ERR_TIMEOUT : CUDADMA_OK;
+}
+
+/* copy between a plain nx x ny x nz array and one padded by four cells on every side */
+int pad_copy(float *padded, float *plain, int nx, int ny, int nz, int z_begin, int z_end, bool to_padded,
+             cudaStream_t s) {
+  const int px = nx + 8, py = ny + 8;
+  cudaMemcpy3DParms p;
+  memset(&p, 0, sizeof(p));
+  cudaPitchedPtr a = make_cudaPitchedPtr(plain, (size_t)nx * 4, (size_t)nx * 4, (size_t)ny);
+  cudaPitchedPtr b = make_cudaPitchedPtr(padded, (size_t)px * 4, (size_t)px * 4, (size_t)py);
+  const cudaPos pa = make_cudaPos(0, 0, (size_t)z_begin), pb = make_cudaPos(16, 4, (size_t)z_begin + 4);
+  p.srcPtr = to_padded ? a : b; p.srcPos = to_padded ? pa : pb;
+  p.dstPtr = to_padded ? b : a; p.dstPos = to_padded ? pb : pa;
+  p.extent = make_cudaExtent((size_t)nx * 4, (size_t)ny, (size_t)(z_end - z_begin));
+  p.kind = cudaMemcpyDeviceToDevice;
+  CK(cudaMemcpy3DAsync(&p, s));
+  return CUDADMA_OK;
+}
+
+/* `steps` steps of the portable kernel on padded copies of the field kept in the workspace */
+int portable_stencil(float *a, float *b, int nx, int ny, int nz, int z_begin, int z_end, const float coeff[5],
+                     int steps, int z_chunk, cudaStream_t s) {
+  if (nx % portable::PS_TX || ny % portable::PS_TY) return CUDADMA_ERR_ARG;
+  const size_t bytes = (size_t)(nx + 8) * (ny + 8) * (nz + 8) * 4;
+  std::lock_guard<std::recursive_mutex> lock(g_ws_mutex);
+  void *pa, *pb;
+  if (int r = ws_get(2, bytes, &pa)) return r;
+  if (int r = ws_get(3, bytes, &pb)) return r;
+  CK(cudaMemsetAsync(pa, 0, bytes, s));
+  CK(cudaMemsetAsync(pb, 0, bytes, s));
+  if (int r = pad_copy((float *)pa, a, nx, ny, nz, 0, nz, true, s)) return r;
+  float *cur = (float *)pa, *nxt = (float *)pb;
+  for (int t = 0; t < steps; ++t) {
+    if (int e = portable::launch_stencil_padded(nxt, cur, nx, ny, nz, z_begin, z_end, coeff, z_chunk, sm_count(), s)) {
+      t_last_cuda_error = e;
+      return CUDADMA_ERR_CUDA;
+    }
+    ++g_launches;
+    float *tmp = cur; cur = nxt; nxt = tmp;
+  }
+  return pad_copy(cur, (steps & 1) ? b : a, nx, ny, nz, z_begin, z_end, false, s);
 }
 
 }  // namespace
@@ -261,6 +304,8 @@ int cudadma_stencil25_step(float *out, const float *in, int nx, int ny, int nz, 
   cudaStream_t s = (cudaStream_t)stream;
   const int sms = sm_count();
   if (sms <= 0) { t_last_cuda_error = (int)cudaErrorNoDevice; return CUDADMA_ERR_CUDA; }
+  if (impl == CUDADMA_IMPL_PORTABLE)
+    return portable_stencil(const_cast<float *>(in), out, nx, ny, nz, z_begin, z_end, coeff, 1, z_chunk, s);
   stencil25::Coeffs k;
   for (int i = 0; i < 5; ++i) k.c[i] = coeff[i];
   const int tiles_x = (nx + stencil25::TILE_X - 1) / stencil25::TILE_X;
@@ -296,6 +341,11 @@ int cudadma_stencil25_step(float *out, const float *in, int nx, int ny, int nz, 
 int cudadma_stencil25_run(float *a, float *b, int nx, int ny, int nz, const float coeff[5], int steps, int impl,
                           void *stream) {
   if (steps < 0) return CUDADMA_ERR_ARG;
+  if (impl == CUDADMA_IMPL_PORTABLE) {
+    if (!a || !b || !coeff || nx <= 0 || ny <= 0 || nz <= 0) return CUDADMA_ERR_ARG;
+    if (sm_count() <= 0) { t_last_cuda_error = (int)cudaErrorNoDevice; return CUDADMA_ERR_CUDA; }
+    return portable_stencil(a, b, nx, ny, nz, 0, nz, coeff, steps, 0, (cudaStream_t)stream);
+  }
   float *cur = a, *nxt = b;
   for (int t = 0; t < steps; ++t) {
     if (int r = cudadma_stencil25_step(nxt, cur, nx, ny, nz, 0, nz, coeff, 0, impl, stream)) return r;
@@ -304,11 +354,29 @@ int cudadma_stencil25_run(float *a, float *b, int nx, int ny, int nz, const floa
   return CUDADMA_OK;
 }
 
+int cudadma_stencil25_step_padded(float *out, const float *in, int nx, int ny, int nz, int z_begin, int z_end,
+                                  const float coeff[5], int z_chunk, int impl, void *stream) {
+  if (!out || !in || !coeff || nx <= 0 || ny <= 0 || nz <= 0 || (nx % portable::PS_TX) || (ny % portable::PS_TY) ||
+      z_begin < 0 || z_end > nz || z_begin > z_end || !aligned16(out) || !aligned16(in) || out == in)
+    return CUDADMA_ERR_ARG;
+  if (impl != CUDADMA_IMPL_PORTABLE) return CUDADMA_ERR_UNSUPPORTED;
+  if (z_begin == z_end) return CUDADMA_OK;
+  const int sms = sm_count();
+  if (sms <= 0) { t_last_cuda_error = (int)cudaErrorNoDevice; return CUDADMA_ERR_CUDA; }
+  if (int e = portable::launch_stencil_padded(out, in, nx, ny, nz, z_begin, z_end, coeff, z_chunk, sms,
+                                              (cudaStream_t)stream)) {
+    t_last_cuda_error = e;
+    return CUDADMA_ERR_CUDA;
+  }
+  ++g_launches;
+  return CUDADMA_OK;
+}
+
 /* ---- host-buffer forms ---- */
 
 int cudadma_seq_copy_host(void *h_dst, const void *h_src, size_t bytes, int chunk_bytes, int impl) {
   if (!h_dst || !h_src) return CUDADMA_ERR_ARG;
-  std::lock_guard<std::mutex> lock(g_ws_mutex);
+  std::lock_guard<std::recursive_mutex> lock(g_ws_mutex);
   cudaStream_t s; void *din, *dout;
   if (int r = ws_stream(&s)) return r;
   if (int r = ws_get(0, bytes, &din)) return r;
@@ -322,7 +390,7 @@ int cudadma_seq_copy_host(void *h_dst, const void *h_src, size_t bytes, int chun
 int cudadma_strided_transpose_host(float *h_dst, const float *h_src, int rows, int cols, int impl) {
   if (!h_dst || !h_src || rows <= 0 || cols <= 0) return CUDADMA_ERR_ARG;
   const size_t bytes = (size_t)rows * cols * 4;
-  std::lock_guard<std::mutex> lock(g_ws_mutex);
+  std::lock_guard<std::recursive_mutex> lock(g_ws_mutex);
   cudaStream_t s; void *din, *dout;
   if (int r = ws_stream(&s)) return r;
   if (int r = ws_get(0, bytes, &din)) return r;
@@ -337,7 +405,7 @@ int cudadma_gather_scatter_host(void *h_out, size_t out_records, const void *h_t
                                 const int32_t *h_gather_idx, const int32_t *h_scatter_idx, size_t n,
                                 int record_bytes, int impl) {
   if (!h_out || !h_table || !h_gather_idx || !h_scatter_idx || record_bytes <= 0) return CUDADMA_ERR_ARG;
-  std::lock_guard<std::mutex> lock(g_ws_mutex);
+  std::lock_guard<std::recursive_mutex> lock(g_ws_mutex);
   cudaStream_t s; void *dtab, *dout, *dg, *ds;
   if (int r = ws_stream(&s)) return r;
   if (int r = ws_get(0, table_records * record_bytes, &dtab)) return r;
@@ -359,7 +427,7 @@ int cudadma_stencil25_run_host(float *h_out, const float *h_in, int nx, int ny, 
                                int steps, int impl) {
   if (!h_out || !h_in || nx <= 0 || ny <= 0 || nz <= 0) return CUDADMA_ERR_ARG;
   const size_t bytes = (size_t)nx * ny * nz * 4;
-  std::lock_guard<std::mutex> lock(g_ws_mutex);
+  std::lock_guard<std::recursive_mutex> lock(g_ws_mutex);
   cudaStream_t s; void *da, *db;
   if (int r = ws_stream(&s)) return r;
   if (int r = ws_get(0, bytes, &da)) return r;
@@ -371,7 +439,7 @@ int cudadma_stencil25_run_host(float *h_out, const float *h_in, int nx, int ny, 
 }
 
 int cudadma_release_workspace(void) {
-  std::lock_guard<std::mutex> lock(g_ws_mutex);
+  std::lock_guard<std::recursive_mutex> lock(g_ws_mutex);
   for (int i = 0; i < 4; ++i) {
     if (g_ws[i]) cudaFree(g_ws[i]);
     g_ws[i] = nullptr; g_ws_bytes[i] = 0;

@@ -120,6 +120,84 @@ transpose_kernel(float *__restrict__ out, const float *__restrict__ in, const in
   }
 }
 
+
+/* Stencil: the reference's stencil example (src/examples/stencil/warp_specialized_manual_buffer.h:
+ * one compute thread per point of a 32 x 16 tile, two CudaDMAStrided objects loading the tile with its
+ * halo, plane after plane, from an array padded with zero cells as src/examples/stencil/cudaDMA_stencil2D.cu:86-97
+ * pads it) with the in-plane average replaced by the radius-4 25-point operator: the z neighbours live in
+ * a per-thread register queue that each thread refills from global memory.
+ * Padded layout: grid cell (x, y, z) is element ((z + 4) * py + (y + 4)) * px + (x + 4), px = nx + 8,
+ * py = ny + 8, all border cells zero. Needs nx % 32 == 0 and ny % 16 == 0. */
+constexpr int PS_TX = 32, PS_TY = 16, PS_R = 4, PS_WX = PS_TX + 2 * PS_R, PS_WY = PS_TY + 2 * PS_R;
+constexpr int PS_COMPUTE = PS_TX * PS_TY, PS_DMA = 64;
+struct PCoeffs { float c[5]; };
+
+__device__ __forceinline__ float stencil_point(const float *__restrict__ w, const float cur, const float (&b)[4],
+                                               const float (&f)[4], const PCoeffs &k) {
+  /* w points at this thread's cell inside the 40 x 24 window */
+  float acc = k.c[0] * cur;
+#pragma unroll
+  for (int r = 1; r <= PS_R; ++r) {
+    const float s = ((w[-r] + w[r]) + (w[-r * PS_WX] + w[r * PS_WX])) + (b[r - 1] + f[r - 1]);
+    acc = fmaf(k.c[r], s, acc);
+  }
+  return acc;
+}
+
+template <int BPT>
+__global__ void __launch_bounds__(PS_COMPUTE + PS_DMA)
+stencil_kernel(float *__restrict__ out, const float *__restrict__ in, const int px, const int py, const int z_begin,
+               const int z_end, const int z_chunk, const PCoeffs k) {
+  __shared__ __align__(128) float buf0[PS_WX * PS_WY];
+  __shared__ __align__(128) float buf1[PS_WX * PS_WY];
+  CudaDMAStrided<true, 16, BPT, PS_WX * 4, PS_DMA, PS_WY> d0(1, PS_COMPUTE, PS_COMPUTE, px * 4, PS_WX * 4);
+  CudaDMAStrided<true, 16, BPT, PS_WX * 4, PS_DMA, PS_WY> d1(2, PS_COMPUTE, PS_COMPUTE, px * 4, PS_WX * 4);
+  const int x0 = blockIdx.x * PS_TX, y0 = blockIdx.y * PS_TY;
+  const int z0 = z_begin + blockIdx.z * z_chunk;
+  const int depth = (z_end - z0 < z_chunk) ? (z_end - z0) : z_chunk;
+  const long long slice = (long long)px * py;
+  if (d0.owns_this_thread()) {
+    const float *win = in + (long long)(z0 + PS_R) * slice + (long long)y0 * px + x0;
+    for (int i = 0; i < depth; i += 2) {
+      d0.execute_dma(win, buf0);
+      win += slice;
+      if (i + 1 < depth) {
+        d1.execute_dma(win, buf1);
+        win += slice;
+      }
+    }
+  } else {
+    const int tx = threadIdx.x % PS_TX, ty = threadIdx.x / PS_TX;
+    const long long cell = (long long)(z0 + PS_R) * slice + (long long)(y0 + ty + PS_R) * px + (x0 + tx + PS_R);
+    const float *p = in + cell;
+    float *o = out + cell;
+    const float *w0 = buf0 + (ty + PS_R) * PS_WX + tx + PS_R;
+    const float *w1 = buf1 + (ty + PS_R) * PS_WX + tx + PS_R;
+    float b[4], f[4], cur = p[0];
+#pragma unroll
+    for (int r = 1; r <= PS_R; ++r) { b[r - 1] = p[-r * slice]; f[r - 1] = p[r * slice]; }
+    d0.start_async_dma();
+    if (depth > 1) d1.start_async_dma();
+    for (int i = 0; i < depth; i += 2) {
+      /* plane z + 5, the next front value, fetched early; not needed (and not there) after the last plane */
+      const float n0 = (i + 1 < depth) ? p[(PS_R + 1) * slice] : 0.0f;
+      d0.wait_for_dma_finish();
+      o[0] = stencil_point(w0, cur, b, f, k);
+      if (i + 2 < depth) d0.start_async_dma();
+      b[3] = b[2]; b[2] = b[1]; b[1] = b[0]; b[0] = cur; cur = f[0]; f[0] = f[1]; f[1] = f[2]; f[2] = f[3]; f[3] = n0;
+      p += slice; o += slice;
+      if (i + 1 < depth) {
+        const float n1 = (i + 2 < depth) ? p[(PS_R + 1) * slice] : 0.0f;
+        d1.wait_for_dma_finish();
+        o[0] = stencil_point(w1, cur, b, f, k);
+        if (i + 3 < depth) d1.start_async_dma();
+        b[3] = b[2]; b[2] = b[1]; b[1] = b[0]; b[0] = cur; cur = f[0]; f[0] = f[1]; f[1] = f[2]; f[2] = f[3]; f[3] = n1;
+        p += slice; o += slice;
+      }
+    }
+  }
+}
+
 /* ---- launchers: return a cudaError_t as int (0 = launched) ---- */
 
 inline int launch_seq_copy(char *dst, const char *src, long long nchunks, int sms, cudaStream_t s) {
@@ -149,6 +227,28 @@ inline int launch_gather_scatter(char *out, const char *table, const int *gidx, 
   const long long want = 6ll * sms;
   const int grid = (int)(nbuf < want ? nbuf : want);
   k<<<grid, GS_THREADS, STAGES * 128 * 32, s>>>(out, table, gidx, sidx, nbuf);
+  return (int)cudaGetLastError();
+}
+
+/* padded arrays (see stencil_kernel); output planes [z_begin, z_end) of the nx x ny x nz grid */
+inline int launch_stencil_padded(float *out, const float *in, int nx, int ny, int nz, int z_begin, int z_end,
+                                 const float coeff[5], int z_chunk, int sms, cudaStream_t s) {
+  if (nx % PS_TX || ny % PS_TY || z_begin < 0 || z_end > nz || z_begin >= z_end) return (int)cudaErrorInvalidValue;
+  PCoeffs k;
+  for (int i = 0; i < 5; ++i) k.c[i] = coeff[i];
+  const int depth = z_end - z_begin;
+  const long long tiles = (long long)(nx / PS_TX) * (ny / PS_TY);
+  if (z_chunk <= 0) {
+    const long long want = 12ll * sms;
+    long long chunks = (want + tiles - 1) / tiles;
+    if (chunks < 1) chunks = 1;
+    z_chunk = (int)((depth + chunks - 1) / chunks);
+    if (z_chunk < 16) z_chunk = 16;
+    if (z_chunk > depth) z_chunk = depth;
+  }
+  dim3 grid(nx / PS_TX, ny / PS_TY, (depth + z_chunk - 1) / z_chunk);
+  stencil_kernel<64><<<grid, PS_COMPUTE + PS_DMA, 0, s>>>(out, in, nx + 2 * PS_R, ny + 2 * PS_R, z_begin, z_end,
+                                                          z_chunk, k);
   return (int)cudaGetLastError();
 }
 

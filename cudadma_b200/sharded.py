@@ -1,0 +1,162 @@
+"""z-sharded 25-point stencil: one process per GPU, radius-wide halo planes
+exchanged between z-neighbours every step and overlapped with the interior.
+
+The reference has no multi-GPU code (every program of it uses device 0,
+src/examples/stencil/cudaDMA_stencil2D.cu:62); this is the driver the sharded
+benchmark configuration needs. Layout per rank: planes [z_lo, z_hi) of the
+global nx x ny x nz grid plus four ghost planes on either side, z slowest, so
+the four boundary planes of a side are one contiguous block. Ghost planes
+beyond the ends of the global grid stay zero, which is the stencil's
+out-of-grid rule.
+
+One step:
+  1. the first and last four owned planes are computed first;
+  2. they are sent to the z-neighbours' ghost planes (torch.distributed
+     send/recv: NCCL over NVLink on GPUs) on a side stream;
+  3. the remaining interior planes are computed meanwhile on the main stream;
+  4. the main stream joins the exchange, buffers swap.
+Every plane is computed by the same kernel with the same arithmetic whatever
+the sharding, so an N-rank run reproduces the 1-rank field bit for bit.
+"""
+import torch
+import torch.distributed as dist
+
+from . import capi
+
+R = 4
+
+
+def slab_bounds(nz, world, rank):
+    """Planes [lo, hi) of rank `rank`: as even as possible, earlier ranks take the remainder."""
+    base, rem = divmod(nz, world)
+    lo = rank * base + min(rank, rem)
+    return lo, lo + base + (1 if rank < rem else 0)
+
+
+def _cuda_step(out, inp, nx, ny, nz_total, z_begin, z_end, coeff):
+    capi.stencil25_step(out, inp, nx, ny, nz_total, z_begin, z_end, coeff)
+
+
+class ShardedStencil:
+    """step_fn(out, inp, nx, ny, nz_total, z_begin, z_end, coeff) computes output planes
+    [z_begin, z_end) of a local array of nz_total planes; the default is the CUDA kernel
+    through the C ABI (there is no CPU path in the product; tests of the host logic on
+    CPU ranks pass their own step function)."""
+
+    def __init__(self, nx, ny, nz, coeff=None, device=None, group=None, step_fn=None, pad_xy=0):
+        """pad_xy: zero cells kept around every plane in x and y (0 for the tensor-map kernel, which
+        needs no border; 4 for kernels that read a padded array). The step function sees the padded
+        planes: nx + 2 * pad_xy by ny + 2 * pad_xy."""
+        self.nx, self.ny, self.nz = nx, ny, nz
+        self.pad = pad_xy
+        self.coeff = tuple(capi.STENCIL_COEFFS if coeff is None else coeff)
+        self.group = group
+        self.distributed = dist.is_available() and dist.is_initialized()
+        self.rank = dist.get_rank(group) if self.distributed else 0
+        self.world = dist.get_world_size(group) if self.distributed else 1
+        self.z_lo, self.z_hi = slab_bounds(nz, self.world, self.rank)
+        self.nzl = self.z_hi - self.z_lo
+        if self.world > 1 and self.nzl < R:
+            raise ValueError("every rank needs at least %d planes (nz=%d over %d ranks)" % (R, nz, self.world))
+        if step_fn is None:
+            if not torch.cuda.is_available():
+                raise RuntimeError("the sharded stencil runs on CUDA devices only; no CPU fallback exists")
+            step_fn = _cuda_step
+            device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+        self.step_fn = step_fn
+        self.device = torch.device("cpu") if device is None else torch.device(device)
+        self.on_cuda = self.device.type == "cuda"
+        self.px, self.py = nx + 2 * pad_xy, ny + 2 * pad_xy
+        plane = self.px * self.py
+        self.plane = plane
+        self.cur = torch.zeros((self.nzl + 2 * R) * plane, dtype=torch.float32, device=self.device)
+        self.nxt = torch.zeros_like(self.cur)
+        self.comm_stream = torch.cuda.Stream(device=self.device) if self.on_cuda and self.world > 1 else None
+        self.steps_done = 0
+
+    # -- data in and out ---------------------------------------------------
+    def owned(self, buf=None):
+        """View [nzl, ny, nx] of the owned cells (no ghost planes, no border) of the current field."""
+        buf = self.cur if buf is None else buf
+        v = buf.view(self.nzl + 2 * R, self.py, self.px)
+        return v[R:R + self.nzl, self.pad:self.pad + self.ny, self.pad:self.pad + self.nx]
+
+    def load(self, slab):
+        """slab: this rank's planes [z_lo, z_hi) as a flat or [nzl, ny, nx] float32 tensor (any device)."""
+        self.cur.zero_()
+        self.nxt.zero_()
+        self.owned().copy_(slab.reshape(self.nzl, self.ny, self.nx), non_blocking=True)
+        self.steps_done = 0
+        if self.world > 1:
+            self._exchange(self.cur, wait=True)
+
+    def store(self, out):
+        out.reshape(self.nzl, self.ny, self.nx).copy_(self.owned(), non_blocking=True)
+
+    # -- halo exchange -----------------------------------------------------
+    def _planes(self, buf, first, count):
+        return buf[first * self.plane:(first + count) * self.plane]
+
+    def _exchange_ops(self, buf):
+        ops = []
+        up, down = self.rank + 1, self.rank - 1
+        if down >= 0:
+            ops.append(dist.P2POp(dist.isend, self._planes(buf, R, R), down, self.group))
+            ops.append(dist.P2POp(dist.irecv, self._planes(buf, 0, R), down, self.group))
+        if up < self.world:
+            ops.append(dist.P2POp(dist.isend, self._planes(buf, self.nzl, R), up, self.group))
+            ops.append(dist.P2POp(dist.irecv, self._planes(buf, R + self.nzl, R), up, self.group))
+        return ops
+
+    def _exchange(self, buf, wait):
+        ops = self._exchange_ops(buf)
+        works = dist.batch_isend_irecv(ops) if ops else []
+        if wait:
+            for w in works:
+                w.wait()
+        return works
+
+    # -- time stepping -----------------------------------------------------
+    def step(self):
+        nx, ny, nzt = self.nx, self.ny, self.nzl + 2 * R
+        cur, nxt = self.cur, self.nxt
+        first, last = R, R + self.nzl  # owned planes are [first, last) of the local array
+        if self.world == 1:
+            self.step_fn(nxt, cur, nx, ny, nzt, first, last, self.coeff)
+        else:
+            lo_end = min(first + R, last)
+            hi_begin = max(last - R, lo_end)
+            self.step_fn(nxt, cur, nx, ny, nzt, first, lo_end, self.coeff)
+            if hi_begin < last:
+                self.step_fn(nxt, cur, nx, ny, nzt, hi_begin, last, self.coeff)
+            if self.on_cuda:
+                main = torch.cuda.current_stream(self.device)
+                self.comm_stream.wait_stream(main)
+                with torch.cuda.stream(self.comm_stream):
+                    works = self._exchange(nxt, wait=False)
+            else:
+                works = self._exchange(nxt, wait=False)
+            if lo_end < hi_begin:
+                self.step_fn(nxt, cur, nx, ny, nzt, lo_end, hi_begin, self.coeff)
+            for w in works:
+                w.wait()  # on CUDA: the main stream waits for the exchange, the host does not block
+            if self.on_cuda:
+                torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
+        self.cur, self.nxt = nxt, cur
+        self.steps_done += 1
+
+    def run(self, steps):
+        for _ in range(steps):
+            self.step()
+        return self.owned()
+
+    def run_host(self, h_out, h_in, steps):
+        """The whole job from and to host memory (pinned tensors copy fastest): upload the slab,
+        `steps` steps, download the slab. Returns when h_out holds the result."""
+        self.load(h_in)
+        self.run(steps)
+        self.store(h_out)
+        if self.on_cuda:
+            torch.cuda.current_stream(self.device).synchronize()
+            if capi.device_status() != 0:
+                raise capi.CudaDMAError("ShardedStencil.run_host", capi.ERR_TIMEOUT, "a wait inside a kernel gave up")

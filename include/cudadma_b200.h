@@ -85,6 +85,16 @@ int cudadma_stencil25_step(float *out, const float *in, int nx, int ny, int nz, 
 int cudadma_stencil25_run(float *a, float *b, int nx, int ny, int nz, const float coeff[5], int steps, int impl,
                           void *stream);
 
+/* The same step on arrays padded by four zero cells on every side, the layout the reference's
+ * stencil example gives its arrays (src/examples/stencil/cudaDMA_stencil2D.cu:86-97): grid cell
+ * (x, y, z) is element ((z + 4) * (ny + 8) + (y + 4)) * (nx + 8) + (x + 4). Only the portable
+ * kernels read this layout (CudaDMAStrided pulls each 40 x 24 window; there is no tensor map to
+ * fill the border); impl must be CUDADMA_IMPL_PORTABLE. nx % 32 == 0, ny % 16 == 0.
+ * With impl = portable, cudadma_stencil25_step/run above copy the field into padded arrays of
+ * the library workspace, run this kernel there and copy the result back. */
+int cudadma_stencil25_step_padded(float *out, const float *in, int nx, int ny, int nz, int z_begin, int z_end,
+                                  const float coeff[5], int z_chunk, int impl, void *stream);
+
 /* Host-buffer forms: the same workloads for callers that hold their data in
  * host memory. Inputs are copied to the device, the kernel runs, the result
  * is copied back; the call returns when the result is in h_* memory. Device

@@ -16,7 +16,8 @@
  *     defined by the benchmark text: radius 4, coefficients c0..c4,
  *     zero outside the domain, ping-pong time steps.
  *
- * Build: see oracle/Makefile (gcc -O3 -fopenmp -shared -fPIC).
+ * Build: see oracle/Makefile (gcc -O3 -ffp-contract=off -fopenmp -shared -fPIC; contraction is
+ * off so that the guarded and the vectorised path of the fp32 step round alike).
  */
 #include <stddef.h>
 #include <stdint.h>

@@ -44,4 +44,11 @@ int cudadma_ref_gather_scatter(void *out, const void *table, const int *gather_i
                                          scatter_idx, (long long)(n / 128), sm_count(), (cudaStream_t)stream);
 }
 
+/* arrays padded by four zero cells on every side: (nx + 8) x (ny + 8) x (nz + 8) floats */
+int cudadma_ref_stencil25_step_padded(float *out, const float *in, int nx, int ny, int nz, int z_begin, int z_end,
+                                      const float coeff[5], int z_chunk, void *stream) {
+  return portable::launch_stencil_padded(out, in, nx, ny, nz, z_begin, z_end, coeff, z_chunk, sm_count(),
+                                         (cudaStream_t)stream);
+}
+
 } /* extern "C" */

@@ -147,6 +147,29 @@ def test_stencil_small(nx, ny, nz, steps):
     assert rel_err(res.cpu().numpy(), exp) <= STENCIL_TOL
 
 
+@pytest.mark.parametrize("nx,ny,nz,steps", [(32, 16, 8, 1), (64, 48, 40, 3), (128, 64, 33, 4)])
+def test_stencil_portable(nx, ny, nz, steps):
+    """The reference-API kernel (padded arrays, CudaDMAStrided window loads) through the same entry point."""
+    field = oracle.fill_uniform(nx * ny * nz, 0xC4, 0.0, 1.0).reshape(nz, ny, nx)
+    a = dev(field)
+    b = torch.zeros_like(a)
+    res = cd.stencil25_run(a, b, nx, ny, nz, steps, impl="portable")
+    status_clean()
+    exp = oracle.stencil25_f64(field, cd.STENCIL_COEFFS, steps)
+    assert rel_err(res.cpu().numpy(), exp) <= STENCIL_TOL
+    # and one step on a plane range, through the padded entry point
+    pad = torch.zeros((nz + 8, ny + 8, nx + 8), dtype=torch.float32, device="cuda")
+    pad[4:-4, 4:-4, 4:-4] = dev(field)
+    out = torch.zeros_like(pad)
+    cd.stencil25_step_padded(out, pad, nx, ny, nz, 1, nz - 1)
+    status_clean()
+    one = oracle.stencil25_f64(field, cd.STENCIL_COEFFS, 1)
+    got = out[4:-4, 4:-4, 4:-4].cpu().numpy()
+    assert rel_err(got[1:nz - 1], one[1:nz - 1]) <= STENCIL_TOL
+    assert not got[0].any() and not got[nz - 1].any()
+    assert not out[:4].any() and not out[:, :4].any() and not out[:, :, :4].any(), "wrote into the border"
+
+
 def test_stencil_plane_ranges_compose():
     """Computing [0, k) and [k, nz) separately equals one full step bit for bit (what the sharded driver relies on)."""
     nx, ny, nz = 64, 32, 50
