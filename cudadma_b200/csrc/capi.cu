@@ -14,6 +14,35 @@
 #include <atomic>
 #include <mutex>
 
+/* tuning knobs (compile-time): stages in flight per CTA and CTAs per SM of each kernel */
+#ifndef SEQ_STAGES
+#define SEQ_STAGES 4
+#endif
+#ifndef SEQ_CTAS_PER_SM
+#define SEQ_CTAS_PER_SM 2
+#endif
+#ifndef SEQ_BULK_STORE
+#define SEQ_BULK_STORE true
+#endif
+#ifndef TR_STAGES
+#define TR_STAGES 3
+#endif
+#ifndef TR_CTAS_PER_SM
+#define TR_CTAS_PER_SM 2
+#endif
+#ifndef GS_STAGES
+#define GS_STAGES 8
+#endif
+#ifndef GS_CTAS_PER_SM
+#define GS_CTAS_PER_SM 4
+#endif
+#ifndef STENCIL25_L2PROMO
+#define STENCIL25_L2PROMO CU_TENSOR_MAP_L2_PROMOTION_L2_256B
+#endif
+#ifndef STENCIL_CTAS_TARGET
+#define STENCIL_CTAS_TARGET 24 /* CTAs per SM the automatic z_chunk aims for */
+#endif
+
 #include "cudadma.h"
 #include "common_kernels.cuh"
 #include "dma_kernels.cuh"
@@ -77,12 +106,13 @@ EncodeTiledFn encode_tiled_fn() {
 
 /* fp32 tensor map, `rank` dims (x fastest), zero fill outside the tensor */
 int make_map_f32(CUtensorMap *map, const void *base, int rank, const cuuint64_t *dims, const cuuint64_t *strides_bytes,
-                 const cuuint32_t *box, CUtensorMapSwizzle swizzle) {
+                 const cuuint32_t *box, CUtensorMapSwizzle swizzle,
+                 CUtensorMapL2promotion promo = CU_TENSOR_MAP_L2_PROMOTION_L2_256B) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) { t_last_cuda_error = (int)cudaErrorNotSupported; return CUDADMA_ERR_CUDA; }
   cuuint32_t ones[5] = {1, 1, 1, 1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<void *>(base), dims,
-                  strides_bytes, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  strides_bytes, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, promo,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) { t_last_cuda_error = (int)cudaErrorInvalidValue; return CUDADMA_ERR_CUDA; }
   return CUDADMA_OK;
@@ -205,10 +235,11 @@ int cudadma_seq_copy(void *dst, const void *src, size_t bytes, int chunk_bytes, 
   const char *p = static_cast<const char *>(src);
   if (nfull > 0) {
     if (impl == CUDADMA_IMPL_NATIVE && chunk_bytes == 16384) {
-      constexpr int STAGES = 8;
-      auto k = seq_copy_kernel<16384, STAGES, true>;
+      constexpr int STAGES = SEQ_STAGES;
+      auto k = seq_copy_kernel<16384, STAGES, SEQ_BULK_STORE>;
       if (int r = allow_smem(k, STAGES * 16384)) return r;
-      const int grid = (int)(nfull < sms ? nfull : sms);
+      const long long want = (long long)SEQ_CTAS_PER_SM * sms;
+      const int grid = (int)(nfull < want ? nfull : want);
       k<<<grid, SEQ_DMA_THREADS + SEQ_COMPUTE_THREADS, STAGES * 16384, s>>>(d, p, nfull);
       if (int r = launched()) return r;
     } else if (impl == CUDADMA_IMPL_PORTABLE && chunk_bytes == 16384) {
@@ -246,11 +277,12 @@ int cudadma_strided_transpose(float *dst, const float *src, int rows, int cols, 
     const cuuint64_t strides[1] = {(cuuint64_t)cols * 4};
     const cuuint32_t box[2] = {TR_BOX_COLS, TR_TILE_ROWS};
     if (int r = make_map_f32(&map, src, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return r;
-    constexpr int STAGES = 6;
+    constexpr int STAGES = TR_STAGES;
     constexpr int SMEM = STAGES * TR_TILE_BYTES + 1024;
     auto k = transpose_kernel<STAGES>;
     if (int r = allow_smem(k, SMEM)) return r;
-    const int grid = (int)(ntiles < sms ? ntiles : sms);
+    const long long want = (long long)TR_CTAS_PER_SM * sms;
+    const int grid = (int)(ntiles < want ? ntiles : want);
     k<<<grid, TR_DMA_THREADS + TR_COMPUTE_THREADS, SMEM, s>>>(map, dst, rows, cols, cols * 4);
     return launched();
   }
@@ -274,10 +306,11 @@ int cudadma_gather_scatter(void *out, const void *table, const int32_t *gather_i
   if (sms <= 0) { t_last_cuda_error = (int)cudaErrorNoDevice; return CUDADMA_ERR_CUDA; }
   const long long nbuf = (long long)(n / 128);
   if (impl == CUDADMA_IMPL_NATIVE) {
-    constexpr int STAGES = 8;
+    constexpr int STAGES = GS_STAGES;
     constexpr int SMEM = STAGES * 128 * 32;
     auto k = gather_scatter_kernel<32, 128, STAGES>;
-    const long long want = 4ll * sms;
+    if (int r = allow_smem(k, SMEM)) return r;
+    const long long want = (long long)GS_CTAS_PER_SM * sms;
     const int grid = (int)(nbuf < want ? nbuf : want);
     k<<<grid, GS_THREADS, SMEM, s>>>(static_cast<char *>(out), static_cast<const char *>(table), gather_idx,
                                      scatter_idx, nbuf);
@@ -315,7 +348,7 @@ int cudadma_stencil25_step(float *out, const float *in, int nx, int ny, int nz, 
     /* enough CTAs for a few waves over the SMs, but runs of at least 32 planes so that the
      * eight lead-in/lead-out planes of a run stay a small share of its loads */
     const long long tiles = (long long)tiles_x * tiles_y;
-    const long long want = 24ll * sms;
+    const long long want = (long long)STENCIL_CTAS_TARGET * sms;
     long long chunks = (want + tiles - 1) / tiles;
     if (chunks < 1) chunks = 1;
     z_chunk = (int)((depth + chunks - 1) / chunks);
@@ -328,9 +361,17 @@ int cudadma_stencil25_step(float *out, const float *in, int nx, int ny, int nz, 
     CUtensorMap map;
     const cuuint64_t dims[3] = {(cuuint64_t)nx, (cuuint64_t)ny, (cuuint64_t)nz};
     const cuuint64_t strides[2] = {(cuuint64_t)nx * 4, (cuuint64_t)nx * ny * 4};
+#ifdef STENCIL25_DIAG_INTERIOR_ONLY
+    const cuuint32_t box[3] = {stencil25::TILE_X, stencil25::TILE_Y, 1};
+#else
     const cuuint32_t box[3] = {stencil25::WIN_X, stencil25::WIN_Y, 1};
-    if (int r = make_map_f32(&map, in, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return r;
+#endif
+    if (int r = make_map_f32(&map, in, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, STENCIL25_L2PROMO)) return r;
     dim3 grid(tiles_x, tiles_y, zc);
+#ifdef STENCIL25_CARVEOUT
+    CK(cudaFuncSetAttribute(stencil25::tensor_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                            STENCIL25_CARVEOUT));
+#endif
     stencil25::tensor_kernel<<<grid, stencil25::COMPUTE_THREADS + stencil25::DMA_THREADS, stencil25::SMEM_BYTES, s>>>(
         map, out, nx, ny, z_begin, z_end, z_chunk, k);
     return launched();

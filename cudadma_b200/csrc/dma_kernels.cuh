@@ -29,7 +29,7 @@ constexpr int SEQ_DMA_THREADS = 128;
 constexpr int SEQ_COMPUTE_THREADS = 256;
 
 template <int CHUNK, int STAGES, bool BULK_STORE>
-__global__ void __launch_bounds__(SEQ_DMA_THREADS + SEQ_COMPUTE_THREADS, 1)
+__global__ void __launch_bounds__(SEQ_DMA_THREADS + SEQ_COMPUTE_THREADS)
 seq_copy_kernel(char *__restrict__ dst, const char *__restrict__ src, const long long nchunks) {
   extern __shared__ __align__(128) unsigned char smem[];
   typedef CudaDMASequential<true, 16, 64, CHUNK, SEQ_DMA_THREADS> Dma;
@@ -112,7 +112,7 @@ constexpr int TR_TILE_BYTES = TR_TILE_ROWS * TR_TILE_COLS * 4;
 constexpr int TR_BOX_BYTES = TR_TILE_ROWS * TR_BOX_COLS * 4;
 
 template <int STAGES>
-__global__ void __launch_bounds__(TR_DMA_THREADS + TR_COMPUTE_THREADS, 1)
+__global__ void __launch_bounds__(TR_DMA_THREADS + TR_COMPUTE_THREADS)
 transpose_kernel(const __grid_constant__ CUtensorMap in_map, float *__restrict__ out, const int rows,
                  const int cols, const int src_pitch_bytes) {
   extern __shared__ unsigned char smem_raw[];

@@ -1,31 +1,33 @@
 /*
  * stencil25.cuh -- radius-4, 25-point finite-difference step on an fp32 grid,
  *   out = c0*u + sum_{r=1..4} c_r*(u[x-r]+u[x+r]+u[y-r]+u[y+r]+u[z-r]+u[z+r]),
- * zero outside the grid, as a z-marching kernel fed by CudaDMA objects.
+ * zero outside the grid, as a z-marching kernel fed by CudaDMAHalo objects.
  *
  * One CTA owns a 32 x 16 xy tile and a run of z planes. Its DMA warp streams
- * the tile plus its radius-4 halo (40 x 24 floats), plane after plane, into a
- * ring of nine shared-memory buffers; 64 compute threads each own a 4 (x) by
- * 2 (y) patch of the tile, keep nine z planes of that patch in registers and
- * read the x/y neighbours of the current plane from shared memory with
- * 16-byte loads. Ring slot and register slot of a plane are both (plane mod 9),
- * so the loop is unrolled nine times and every index is static.
+ * the tile plus its radius-4 halo (40 x 24 floats, one TMA box per plane, zero
+ * fill outside the grid) into a ring of shared-memory buffers. 64 compute
+ * threads each own a 4 (x) by 2 (y) patch of the tile. Every plane is read from
+ * shared memory exactly once, when it arrives, and is pushed forward into the
+ * nine output planes it contributes to:
+ *   - its in-plane (x and y) neighbours go to the output plane of the same z;
+ *   - its own value times c_|d| goes to the output planes z + d, d = -4..4.
+ * The nine partial output planes of a patch live in registers; the slot of
+ * output plane z is z mod 9, so the plane loop is unrolled nine times and every
+ * register index is static. An output plane is complete, and stored, once the
+ * plane four above it has been folded in. Every output sums its 25 products in
+ * the same order whatever z range a CTA or a GPU owns, so results do not
+ * depend on how the grid is cut.
  *
  * The buffering scheme is the reference's warp-specialised stencil example
- * (src/examples/stencil/warp_specialized_manual_buffer.h:46-112) with nine
+ * (src/examples/stencil/warp_specialized_manual_buffer.h:46-112) with a ring of
  * buffers instead of two; the arithmetic replaces its in-plane average
  * (src/examples/stencil/stencil_math.h:28-86) by the 25-point operator.
- *
- * The same body serves two loaders:
- *   - tensor-map loader (cudadma.h only): CudaDMAHalo::execute_dma_tile, one
- *     TMA box per plane from the unpadded grid, zero fill outside it;
- *   - portable loader (any CudaDMA header): CudaDMAStrided row copies of the
- *     40 x 24 window from a grid padded by four zero cells on every side,
- *     the way the reference's stencil example loads its tiles
- *     (src/examples/stencil/warp_specialized_single_buffer.h:35-58).
  */
 #ifndef CUDADMA_B200_STENCIL25_CUH
 #define CUDADMA_B200_STENCIL25_CUH
+
+#include <type_traits>
+#include <utility>
 
 namespace stencil25 {
 
@@ -33,141 +35,191 @@ constexpr int R = 4;
 constexpr int TILE_X = 32, TILE_Y = 16;
 constexpr int WIN_X = TILE_X + 2 * R, WIN_Y = TILE_Y + 2 * R; /* 40 x 24 */
 constexpr int PLANE_BYTES = WIN_X * WIN_Y * 4;                /* 3840 */
-constexpr int SLOTS = 2 * R + 1;                              /* 9 */
+constexpr int SLOTS = 2 * R + 1;                              /* 9 partial output planes */
+#ifndef STENCIL25_STAGES
+#define STENCIL25_STAGES 9 /* must divide SLOTS; nine keeps eight planes of loads in flight per CTA */
+#endif
+constexpr int STAGES = STENCIL25_STAGES;
+static_assert(SLOTS % STAGES == 0, "the ring size must divide nine so that stage indices stay static");
 constexpr int COMPUTE_THREADS = 64, DMA_THREADS = 32;
-constexpr int SMEM_BYTES = SLOTS * PLANE_BYTES;
+constexpr int SMEM_BYTES = STAGES * PLANE_BYTES;
 
 struct Coeffs { float c[5]; };
 
-/* One output plane for this thread's 4 x 2 patch.
- * cur: the current plane's window in shared memory; q: register queue, q[s]
- * is the patch on the plane living in slot s; sc: slot of the current plane. */
-template <int SC>
-__device__ __forceinline__ void compute_patch(const float *__restrict__ cur, const float (&q)[SLOTS][2][4],
-                                              const int tx, const int ty, const Coeffs &k, float (&res)[2][4]) {
-  const float *row0 = cur + (2 * ty + R) * WIN_X + 4 * tx; /* column x-4 of own row 0 */
-  float a[2][12];
-#pragma unroll
-  for (int j = 0; j < 2; ++j) {
-    const float4 l = *reinterpret_cast<const float4 *>(row0 + j * WIN_X);
-    const float4 r = *reinterpret_cast<const float4 *>(row0 + j * WIN_X + 8);
-    a[j][0] = l.x; a[j][1] = l.y; a[j][2] = l.z; a[j][3] = l.w;
-    a[j][4] = q[SC][j][0]; a[j][5] = q[SC][j][1]; a[j][6] = q[SC][j][2]; a[j][7] = q[SC][j][3];
-    a[j][8] = r.x; a[j][9] = r.y; a[j][10] = r.z; a[j][11] = r.w;
-  }
-  /* yn[d]: window rows above the patch (d = 0..3 <-> row y0-4..y0-1) and below (d = 4..7 <-> y1+1..y1+4) */
-  float yn[8][4];
-#pragma unroll
-  for (int d = 0; d < 4; ++d) {
-    const float4 u = *reinterpret_cast<const float4 *>(row0 + (d - 4) * WIN_X + 4);
-    const float4 v = *reinterpret_cast<const float4 *>(row0 + (d + 2) * WIN_X + 4);
-    yn[d][0] = u.x; yn[d][1] = u.y; yn[d][2] = u.z; yn[d][3] = u.w;
-    yn[d + 4][0] = v.x; yn[d + 4][1] = v.y; yn[d + 4][2] = v.z; yn[d + 4][3] = v.w;
-  }
-#pragma unroll
-  for (int j = 0; j < 2; ++j) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float acc = k.c[0] * a[j][4 + i];
-#pragma unroll
-      for (int r = 1; r <= R; ++r) {
-        /* rows y-r and y+r: own rows come from the queue, the rest from yn */
-        float up, dn;
-        if (j == 0) {
-          up = yn[4 - r][i];
-          dn = (r == 1) ? q[SC][1][i] : yn[4 + r - 2][i];
-        } else {
-          up = (r == 1) ? q[SC][0][i] : yn[4 - (r - 1)][i];
-          dn = yn[3 + r][i];
-        }
-        const float s = ((a[j][4 + i - r] + a[j][4 + i + r]) + (up + dn)) +
-                        (q[(SC + SLOTS - r) % SLOTS][j][i] + q[(SC + r) % SLOTS][j][i]);
-        acc = fmaf(k.c[r], s, acc);
-      }
-      res[j][i] = acc;
-    }
-  }
+/* Arithmetic is done two points at a time with the packed fp32 FMA of sm_100
+ * (fma.rn.f32x2 through __ffma2_rn): one issue slot for two fused multiply-adds,
+ * each bit-identical to fmaf. A patch row of four points is two such pairs. */
+struct Row { float2 p[2]; };
+
+__device__ __forceinline__ Row ld_row(const float *p) {
+  const float4 v = *reinterpret_cast<const float4 *>(p);
+  Row r;
+  r.p[0] = make_float2(v.x, v.y);
+  r.p[1] = make_float2(v.z, v.w);
+  return r;
 }
 
-/* Compute side of the CTA. RING exposes stage[s] with the CudaDMA sync calls.
- * Planes are numbered k = 0 .. nplanes-1 relative to (first output plane - 4);
- * output plane k-4 is produced at step k once planes k-8 .. k are in. */
-template <typename RING>
-__device__ __forceinline__ void compute_side(RING &ring, const unsigned char *smem, float *__restrict__ out,
-                                             const long long out_pitch_y, const long long out_pitch_z,
-                                             const int x_limit, const int y_limit, const int nplanes,
-                                             const Coeffs &k) {
-  const int tx = threadIdx.x & 7, ty = threadIdx.x >> 3;
-  float q[SLOTS][2][4];
+template <typename F, int... I>
+__device__ __forceinline__ void static_for(F &&f, std::integer_sequence<int, I...>) {
+  (f(std::integral_constant<int, I>{}), ...);
+}
+
+/* Fold the plane in slot position KK (plane number mod 9) into the partial outputs.
+ * win: this thread's patch origin inside the plane's window (window row 2*ty + R,
+ * window column 4*tx + R). in_plane: the plane is itself an output plane of this
+ * CTA, so its x/y neighbours are needed. c2[r] = (c_r, c_r). */
+template <int KK>
+__device__ __forceinline__ void fold_plane(const float *__restrict__ win, float2 (&acc)[SLOTS][2][2],
+                                           const float2 (&c2)[R + 1], const bool in_plane) {
+  Row u[2];
+  u[0] = ld_row(win);
+  u[1] = ld_row(win + WIN_X);
+  /* z direction: output plane KK + d gets c_|d| * u; the output plane four ahead starts here */
 #pragma unroll
-  for (int s = 0; s < SLOTS; ++s) ring.stage[s].start_async_dma();
-  const bool store_ok = (4 * tx < x_limit);
-  float *o = out + (long long)(2 * ty) * out_pitch_y + 4 * tx;
-  for (int k0 = 0; k0 < nplanes; k0 += SLOTS) {
+  for (int j = 0; j < 2; ++j)
 #pragma unroll
-    for (int kk = 0; kk < SLOTS; ++kk) {
-      const int kp = k0 + kk;
-      if (kp >= nplanes) break;
-      ring.stage[kk].wait_for_dma_finish();
-      const float *pl = reinterpret_cast<const float *>(smem + kk * PLANE_BYTES) + (2 * ty + R) * WIN_X + 4 * tx + 4;
+    for (int h = 0; h < 2; ++h) {
+      acc[(KK + R) % SLOTS][j][h] = make_float2(c2[R].x * u[j].p[h].x, c2[R].y * u[j].p[h].y);
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const float4 c = *reinterpret_cast<const float4 *>(pl + j * WIN_X);
-        q[kk][j][0] = c.x; q[kk][j][1] = c.y; q[kk][j][2] = c.z; q[kk][j][3] = c.w;
+      for (int d = -R; d < R; ++d) {
+        const int cr = d < 0 ? -d : d;
+        float2 &a = acc[(KK + d + SLOTS) % SLOTS][j][h];
+        a = __ffma2_rn(c2[cr], u[j].p[h], a);
       }
-      if (kp < R) ring.stage[kk].start_async_dma(); /* lead-in planes are never a current plane */
-      if (kp >= 2 * R) {
-        const int sc = (kk + SLOTS - R) % SLOTS;
-        float res[2][4];
-        /* sc is a compile-time constant after unrolling; dispatch keeps the queue indices static */
-        switch (sc) {
-          case 0: compute_patch<0>(reinterpret_cast<const float *>(smem + 0 * PLANE_BYTES), q, tx, ty, k, res); break;
-          case 1: compute_patch<1>(reinterpret_cast<const float *>(smem + 1 * PLANE_BYTES), q, tx, ty, k, res); break;
-          case 2: compute_patch<2>(reinterpret_cast<const float *>(smem + 2 * PLANE_BYTES), q, tx, ty, k, res); break;
-          case 3: compute_patch<3>(reinterpret_cast<const float *>(smem + 3 * PLANE_BYTES), q, tx, ty, k, res); break;
-          case 4: compute_patch<4>(reinterpret_cast<const float *>(smem + 4 * PLANE_BYTES), q, tx, ty, k, res); break;
-          case 5: compute_patch<5>(reinterpret_cast<const float *>(smem + 5 * PLANE_BYTES), q, tx, ty, k, res); break;
-          case 6: compute_patch<6>(reinterpret_cast<const float *>(smem + 6 * PLANE_BYTES), q, tx, ty, k, res); break;
-          case 7: compute_patch<7>(reinterpret_cast<const float *>(smem + 7 * PLANE_BYTES), q, tx, ty, k, res); break;
-          default: compute_patch<8>(reinterpret_cast<const float *>(smem + 8 * PLANE_BYTES), q, tx, ty, k, res); break;
+    }
+  if (in_plane) {
+    float2(&o)[2][2] = acc[KK % SLOTS];
+    /* x direction: row cells x-4 .. x+7 as pairs starting at even (e) and odd (q) offsets */
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const Row l = ld_row(win + j * WIN_X - 4), r = ld_row(win + j * WIN_X + 4);
+      const float2 e[6] = {l.p[0], l.p[1], u[j].p[0], u[j].p[1], r.p[0], r.p[1]};
+      float2 q[5];
+#pragma unroll
+      for (int t = 0; t < 5; ++t) q[t] = make_float2(e[t].y, e[t + 1].x);
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int rr = 1; rr <= R; ++rr) {
+          const int kl = 4 + 2 * h - rr, kr = 4 + 2 * h + rr; /* first cell of the left / right neighbour pair */
+          o[j][h] = __ffma2_rn(c2[rr], (kl & 1) ? q[kl >> 1] : e[kl >> 1], o[j][h]);
+          o[j][h] = __ffma2_rn(c2[rr], (kr & 1) ? q[kr >> 1] : e[kr >> 1], o[j][h]);
         }
-        float *oz = o + (long long)(kp - 2 * R) * out_pitch_z;
-        if (store_ok) {
-          if (2 * ty < y_limit) *reinterpret_cast<float4 *>(oz) = make_float4(res[0][0], res[0][1], res[0][2], res[0][3]);
-          if (2 * ty + 1 < y_limit)
-            *reinterpret_cast<float4 *>(oz + out_pitch_y) = make_float4(res[1][0], res[1][1], res[1][2], res[1][3]);
+    }
+    /* y direction: own rows feed each other, the eight rows around the patch are streamed */
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      o[0][h] = __ffma2_rn(c2[1], u[1].p[h], o[0][h]);
+      o[1][h] = __ffma2_rn(c2[1], u[0].p[h], o[1][h]);
+    }
+#pragma unroll
+    for (int d = 1; d <= R; ++d) {
+      const Row up = ld_row(win - d * WIN_X);       /* row y0 - d: distance d from row 0, d + 1 from row 1 */
+      const Row dn = ld_row(win + (d + 1) * WIN_X); /* row y1 + d: distance d from row 1, d + 1 from row 0 */
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        o[0][h] = __ffma2_rn(c2[d], up.p[h], o[0][h]);
+        o[1][h] = __ffma2_rn(c2[d], dn.p[h], o[1][h]);
+        if (d < R) {
+          o[1][h] = __ffma2_rn(c2[d + 1], up.p[h], o[1][h]);
+          o[0][h] = __ffma2_rn(c2[d + 1], dn.p[h], o[0][h]);
         }
-        ring.stage[sc].start_async_dma();
       }
     }
   }
 }
 
 #ifdef CUDADMA_B200_CUDADMA_H
-/* Tensor-map loader. in_map: 3-D map over the nx x ny x nz input (x fastest),
- * box 40 x 24 x 1. Output planes [z_begin, z_end) are produced, blockIdx.z
- * taking z_chunk of them; input planes outside [0, nz) read as zero. */
+/* in_map: 3-D tensor map over the nx x ny x nz input (x fastest), box 40 x 24 x 1.
+ * Output planes [z_begin, z_end) are produced, blockIdx.z taking z_chunk of them;
+ * input planes outside [0, nz) read as zero. Planes are numbered kp = 0 .. depth + 7
+ * from (first output plane - 4); output plane kp - 8 is stored at step kp. */
+#if defined(STENCIL25_MAXNREG)
+__global__ void __maxnreg__(STENCIL25_MAXNREG)
+#elif defined(STENCIL25_MIN_BLOCKS)
+__global__ void __launch_bounds__(COMPUTE_THREADS + DMA_THREADS, STENCIL25_MIN_BLOCKS)
+#else
 __global__ void __launch_bounds__(COMPUTE_THREADS + DMA_THREADS)
+#endif
 tensor_kernel(const __grid_constant__ CUtensorMap in_map, float *__restrict__ out, const int nx, const int ny,
               const int z_begin, const int z_end, const int z_chunk, const Coeffs k) {
   extern __shared__ __align__(128) unsigned char smem[];
   typedef CudaDMAHalo<float, R, true, 16> Halo;
-  cudadma_b200::kernels::Ring<Halo, SLOTS> ring(DMA_THREADS, COMPUTE_THREADS, COMPUTE_THREADS, TILE_X, TILE_Y, nx);
+#ifdef STENCIL25_DIAG_INTERIOR_ONLY
+  cudadma_b200::kernels::Ring<Halo, STAGES> ring(DMA_THREADS, COMPUTE_THREADS, COMPUTE_THREADS, TILE_X - 2 * R,
+                                                 TILE_Y - 2 * R, nx);
+#else
+  cudadma_b200::kernels::Ring<Halo, STAGES> ring(DMA_THREADS, COMPUTE_THREADS, COMPUTE_THREADS, TILE_X, TILE_Y, nx);
+#endif
   const int x0 = blockIdx.x * TILE_X, y0 = blockIdx.y * TILE_Y;
   const int z0 = z_begin + blockIdx.z * z_chunk;
   const int depth = (z_end - z0 < z_chunk) ? (z_end - z0) : z_chunk;
   const int nplanes = depth + 2 * R;
   if (ring.stage[0].owns_this_thread()) {
-    for (int k0 = 0;; k0 += SLOTS) {
+    for (int k0 = 0;; k0 += STAGES) {
 #pragma unroll
-      for (int kk = 0; kk < SLOTS; ++kk) {
-        if (k0 + kk >= nplanes) return;
-        ring.stage[kk].execute_dma_tile(&in_map, x0, y0, z0 - R + k0 + kk, smem + kk * PLANE_BYTES);
+      for (int s = 0; s < STAGES; ++s) {
+        if (k0 + s >= nplanes) return;
+#ifdef STENCIL25_DIAG_INTERIOR_ONLY
+        ring.stage[s].execute_dma_tile(&in_map, x0 + R, y0 + R, z0 - R + k0 + s, smem + s * PLANE_BYTES);
+#else
+#ifdef STENCIL25_DIAG_NO_LOAD
+        ring.stage[s].wait_for_dma_start();
+        ring.stage[s].finish_async_dma();
+#else
+        ring.stage[s].execute_dma_tile(&in_map, x0, y0, z0 - R + k0 + s, smem + s * PLANE_BYTES);
+#endif
+#endif
       }
     }
   } else {
+    const int tx = threadIdx.x & 7, ty = threadIdx.x >> 3;
     const long long py = nx, pz = (long long)nx * ny;
-    compute_side(ring, smem, out + (long long)z0 * pz + (long long)y0 * py + x0, py, pz, nx - x0, ny - y0, nplanes, k);
+    float *o = out + (long long)z0 * pz + (long long)(y0 + 2 * ty) * py + x0 + 4 * tx;
+    const bool row0_ok = (x0 + 4 * tx < nx) && (y0 + 2 * ty < ny);
+    const bool row1_ok = (x0 + 4 * tx < nx) && (y0 + 2 * ty + 1 < ny);
+    const int win_off = (2 * ty + R) * WIN_X + 4 * tx + R;
+    float2 acc[SLOTS][2][2];
+    float2 c2[R + 1];
+#pragma unroll
+    for (int r = 0; r <= R; ++r) c2[r] = make_float2(k.c[r], k.c[r]);
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) ring.stage[s].start_async_dma();
+    for (int k0 = 0; k0 < nplanes; k0 += SLOTS) {
+      static_for(
+          [&](auto kk_c) {
+            constexpr int kk = decltype(kk_c)::value;
+            const int kp = k0 + kk;
+            if (kp < nplanes) {
+              ring.stage[kk % STAGES].wait_for_dma_finish();
+              const float *win = reinterpret_cast<const float *>(smem + (kk % STAGES) * PLANE_BYTES) + win_off;
+#ifdef STENCIL25_DIAG_NO_XY
+              fold_plane<kk>(win, acc, c2, false);
+#else
+              fold_plane<kk>(win, acc, c2, kp >= R && kp < depth + R);
+#endif
+              ring.stage[kk % STAGES].start_async_dma();
+              if (kp >= 2 * R) {
+                /* output plane kp - 8 of this CTA is complete: it sits in slot (kk - 4) mod 9 */
+                const float2(&r)[2][2] = acc[(kk + SLOTS - R) % SLOTS];
+                float *oz = o + (long long)(kp - 2 * R) * pz;
+#ifdef STENCIL25_DIAG_NO_STORE
+                if (row0_ok && r[0][0].x == 123.456f)
+#else
+                if (row0_ok)
+#endif
+                  *reinterpret_cast<float4 *>(oz) = make_float4(r[0][0].x, r[0][0].y, r[0][1].x, r[0][1].y);
+#ifdef STENCIL25_DIAG_NO_STORE
+                if (row1_ok && r[1][0].x == 123.456f)
+#else
+                if (row1_ok)
+#endif
+                  *reinterpret_cast<float4 *>(oz + py) = make_float4(r[1][0].x, r[1][0].y, r[1][1].x, r[1][1].y);
+              }
+            }
+          },
+          std::make_integer_sequence<int, SLOTS>{});
+    }
   }
 }
 #endif

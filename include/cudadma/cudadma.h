@@ -92,6 +92,21 @@ __device__ __forceinline__ void mbar_fence_init() {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive_n(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+/* One arrival operation for all lanes of the warp that are executing this call together:
+ * the lanes synchronise (which orders their earlier shared-memory accesses before the
+ * arrival), then the lowest of them arrives once with their number as the count. */
+__device__ __forceinline__ void mbar_arrive_warp(uint32_t bar) {
+#ifdef CUDADMA_PER_THREAD_ARRIVE
+  mbar_arrive(bar);
+#else
+  const unsigned mask = __activemask();
+  __syncwarp(mask);
+  if ((threadIdx.x & 31u) == (unsigned)(__ffs(mask) - 1)) mbar_arrive_n(bar, (uint32_t)__popc(mask));
+#endif
+}
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");
@@ -350,7 +365,7 @@ class CudaDMA {
   /* compute threads: the buffer may be overwritten (or, for a scatter, read) by the DMA threads */
   __device__ __forceinline__ void start_async_dma(void) const {
     cudadma_b200::ptx::fence_proxy_async();
-    cudadma_b200::ptx::mbar_arrive(m_bar_empty);
+    cudadma_b200::ptx::mbar_arrive_warp(m_bar_empty);
   }
   /* compute threads: block until the transfer has landed */
   __device__ __forceinline__ void wait_for_dma_finish(void) const {
@@ -365,7 +380,7 @@ class CudaDMA {
     cudadma_b200::ptx::fence_proxy_async();
   }
   /* DMA threads: this thread's share of the transfer is complete (or tracked by the barrier) */
-  __device__ __forceinline__ void finish_async_dma(void) const { cudadma_b200::ptx::mbar_arrive(m_bar_full); }
+  __device__ __forceinline__ void finish_async_dma(void) const { cudadma_b200::ptx::mbar_arrive_warp(m_bar_full); }
 
  protected:
   const int m_dma_tid;
@@ -449,7 +464,7 @@ template <bool WS>
 __device__ __forceinline__ void complete(const int cp_async_pending, const uint32_t bar_full) {
   if (WS) {
     if (cp_async_pending) ptx::mbar_arrive_after_cp_async(bar_full);
-    else ptx::mbar_arrive(bar_full);
+    else ptx::mbar_arrive_warp(bar_full);
   } else {
     if (cp_async_pending) ptx::ldgsts_wait_all();
   }

@@ -51,7 +51,16 @@ def test_gather_scatter_matches_reference_build():
     ref.gather_scatter(a, table, g, s, n)
     cd.gather_scatter(b, table, g, s, n, 32, "portable")
     cd.gather_scatter(c, table, g, s, n, 32, "native")
-    assert torch.equal(a, b) and torch.equal(a, c)
+    exp = oracle.gather_scatter(np.zeros(n * 8, dtype=np.float32), table.cpu().numpy(), g.cpu().numpy(),
+                                s.cpu().numpy())
+    assert np.array_equal(b.cpu().numpy().view(np.uint32), exp.view(np.uint32))
+    assert torch.equal(b, c)
+    if not torch.equal(a, b):
+        # The reference's warp-specialised execute_dma loads its source before it waits for the compute
+        # threads' start signal (start_xfer_async precedes wait_for_dma_start, include/cudaDMAv2.h:1461-1475).
+        # That is harmless for a gather from global memory, but the scatter object then reads the shared
+        # buffer before the gather that fills it has been handed over. No reference test runs a scatter.
+        pytest.xfail("reference scatter reads its shared-memory source before the handshake")
 
 
 def test_stencil_matches_reference_build():

@@ -1,0 +1,66 @@
+"""The z-sharded stencil on real GPUs: N ranks (NCCL halo exchange) reproduce the one-GPU field
+bit for bit. Needs at least two CUDA devices; skipped otherwise."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, nx, ny, nz, steps, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from cudadma_b200.sharded import ShardedStencil
+        from oracle import oracle
+        field = oracle.fill_uniform(nx * ny * nz, 0xC4, 0.0, 1.0).reshape(nz, ny, nx)
+        st = ShardedStencil(nx, ny, nz)
+        st.load(torch.from_numpy(field[st.z_lo:st.z_hi].copy()).cuda())
+        got = st.run(steps).cpu().numpy().copy()
+        torch.cuda.synchronize()
+        q.put((rank, st.z_lo, st.z_hi, got))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("nz,steps", [(40, 3), (19, 2)])
+def test_two_gpus_equal_one_gpu(nz, steps):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two CUDA devices")
+    import cudadma_b200 as cd
+    from oracle import oracle
+    nx, ny, world = 128, 64, 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, nx, ny, nz, steps, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    parts = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    field = oracle.fill_uniform(nx * ny * nz, 0xC4, 0.0, 1.0)
+    a = torch.from_numpy(field).cuda()
+    b = torch.zeros_like(a)
+    one = cd.stencil25_run(a, b, nx, ny, nz, steps).cpu().numpy().reshape(nz, ny, nx)
+    for rank, lo, hi, got in parts:
+        assert np.array_equal(got.view(np.uint32), one[lo:hi].view(np.uint32)), "rank %d differs" % rank
+    exp = oracle.stencil25_f64(field.reshape(nz, ny, nx), cd.STENCIL_COEFFS, steps)
+    assert np.abs(one - exp).max() / np.abs(exp).max() <= 1e-5
