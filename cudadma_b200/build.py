@@ -3,8 +3,10 @@
   cudadma_b200/libcudadma_b200.so      the product: kernels + C ABI (nvcc, sm_100a)
   tests/csrc/libcudadma_apitest.so     test kernels that drive the object API one CTA at a time
   oracle/liboracle.so                  CPU oracle (gcc)
-  oracle/_ref/*.so                     the reference CudaDMA headers compiled for sm_100a
-                                       (only where the reference checkout is present)
+  oracle/_ref/libcudadma_ref.so        the benchmark workloads through the reference CudaDMA
+                                       headers compiled for sm_100a (only where the reference
+                                       checkout is present; `make -C oracle ref-apitest` adds the
+                                       API harness against the reference, which takes very long)
 
 nvcc cross-compiles without a GPU; nothing here needs one.
 """

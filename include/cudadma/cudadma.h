@@ -652,8 +652,8 @@ class CudaDMASequential<DO_SYNC, 0, 0, 0, 0> {
 /* ------------------------------------------------------------------------- */
 /* CudaDMAStrided: NUM_ELMTS rows of BYTES_PER_ELMT bytes, independent source */
 /* and destination row strides in bytes (cudaDMAv2.h:3193-3195).              */
-/* Constructor forms (s = one stride: source stride, destination packed;      */
-/* s,d = both strides):                                                       */
+/* Constructor forms (s = one stride, used for source and destination alike,  */
+/* cudaDMAv2.h:5110-5127; s,d = source and destination stride):               */
 /*   ws  L1 (dmaID, ndma, ncomp, start, elmt_bytes, num_elmts, s | s, d)      */
 /*   ws  L2 (dmaID, ndma, ncomp, start, num_elmts, s | s, d)                  */
 /*   ws  L3 (dmaID, ncomp, start, num_elmts, s | s, d)                        */
@@ -686,7 +686,7 @@ class CudaDMAStrided : public CudaDMA {
       else if (LEVEL <= 3) { p.bytes = BYTES_PER_ELMT; p.rows = a[k]; k += 1; }
       else { p.bytes = BYTES_PER_ELMT; p.rows = NUM_ELMTS; }
       p.sstride = a[k];
-      p.dstride = (n - k >= 2) ? a[k + 1] : p.bytes;
+      p.dstride = (n - k >= 2) ? a[k + 1] : p.sstride;
     } else {
       int k = 0;
       if (LEVEL == 1) { p.bytes = a[0]; p.rows = a[1]; k = 2; }
@@ -694,7 +694,7 @@ class CudaDMAStrided : public CudaDMA {
       else { p.bytes = BYTES_PER_ELMT; p.rows = NUM_ELMTS; }
       p.sstride = a[k];
       const bool two = (n - k >= 2);
-      p.dstride = two ? a[k + 1] : p.bytes;
+      p.dstride = two ? a[k + 1] : p.sstride;
       int nd = DMA_THREADS, st = 0;
       if (two) {
         if (LEVEL <= 2) { nd = a[k + 2]; st = a[k + 3]; }
