@@ -14,6 +14,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libcudadma_b200.so")
 
 OK, ERR_ARG, ERR_CUDA, ERR_UNSUPPORTED, ERR_NOMEM, ERR_TIMEOUT = 0, -1, -2, -3, -4, 1
+ERR_TOO_LARGE = -5
 IMPL_NATIVE, IMPL_PORTABLE = 0, 1
 _IMPLS = {"native": IMPL_NATIVE, "portable": IMPL_PORTABLE, IMPL_NATIVE: IMPL_NATIVE, IMPL_PORTABLE: IMPL_PORTABLE}
 
@@ -38,6 +39,8 @@ SYMBOLS = [
     ("cudadma_stencil25_step_padded", _c.c_int,
      [_c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.POINTER(_c.c_float), _c.c_int,
       _c.c_int, _c.c_void_p]),
+    ("cudadma_stencil25_step_noalloc", _c.c_int,
+     [_c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.POINTER(_c.c_float), _c.c_void_p]),
     ("cudadma_seq_copy_host", _c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_int, _c.c_int]),
     ("cudadma_strided_transpose_host", _c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int]),
     ("cudadma_gather_scatter_host", _c.c_int,
@@ -177,6 +180,16 @@ def stencil25_step_padded(out, inp, nx, ny, nz, z_begin=0, z_end=None, coeff=Non
     _check("cudadma_stencil25_step_padded",
            lib().cudadma_stencil25_step_padded(_ptr(out), _ptr(inp), nx, ny, nz, z_begin, z_end, _coeffs(coeff),
                                                z_chunk, _IMPLS[impl], _stream(stream)))
+
+
+def stencil25_step_noalloc(out, inp, nx, ny, nz, coeff=None, stream=None):
+    """One full step through the entry point that allocates no device memory: for solvers whose
+    framework owns all device memory, or whose time-step loop cannot afford the device-wide stall
+    of cudaMalloc. The padded grid is limited to 2**21 cells; larger grids raise with status
+    ERR_TOO_LARGE. Calls share one built-in scratch array, so keep them ordered on the GPU."""
+    _require_cuda(out, inp)
+    _check("cudadma_stencil25_step_noalloc",
+           lib().cudadma_stencil25_step_noalloc(_ptr(out), _ptr(inp), nx, ny, nz, _coeffs(coeff), _stream(stream)))
 
 
 def stencil25_run(a, b, nx, ny, nz, steps, coeff=None, impl="native", stream=None):

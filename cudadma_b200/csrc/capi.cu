@@ -208,6 +208,7 @@ const char *cudadma_status_string(int status) {
     case CUDADMA_ERR_UNSUPPORTED: return "implementation not available";
     case CUDADMA_ERR_NOMEM: return "out of device or pinned memory";
     case CUDADMA_ERR_TIMEOUT: return "a bounded wait inside the kernel gave up";
+    case CUDADMA_ERR_TOO_LARGE: return "grid larger than the built-in scratch of the entry point that allocates nothing";
     default: return "unknown status";
   }
 }
@@ -477,6 +478,65 @@ int cudadma_stencil25_run_host(float *h_out, const float *h_in, int nx, int ny, 
   if (int r = cudadma_stencil25_run((float *)da, (float *)db, nx, ny, nz, coeff, steps, impl, s)) return r;
   CK(cudaMemcpyAsync(h_out, (steps & 1) ? db : da, bytes, cudaMemcpyDeviceToHost, s));
   return finish_status(s);
+}
+
+/* ---- the entry point that allocates nothing ---- */
+
+}  /* extern "C" */
+
+namespace {
+/* Scratch of cudadma_stencil25_step_noalloc: two padded copies of the field, side by side.
+ * It is part of the library image, so every GPU that loads the library holds these 16 MiB
+ * until the process exits, used or not. */
+constexpr size_t NOALLOC_MAX_FLOATS = (size_t)1 << 21; /* per padded array */
+static __device__ __align__(256) float g_noalloc_scratch[2 * NOALLOC_MAX_FLOATS];
+
+/* In host code the name g_noalloc_scratch is only a handle for the runtime, not a device
+ * address: the address is asked for once per device, with that device current. */
+constexpr int NOALLOC_MAX_DEVICES = 64;
+std::mutex g_noalloc_mutex;
+float *g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {nullptr};
+
+int noalloc_scratch(float **out) {
+  int dev = -1;
+  CK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return CUDADMA_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (!g_noalloc_ptr[dev]) {
+    void *p = nullptr;
+    CK(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+    g_noalloc_ptr[dev] = static_cast<float *>(p);
+  }
+  *out = g_noalloc_ptr[dev];
+  return CUDADMA_OK;
+}
+}  // namespace
+
+extern "C" {
+
+int cudadma_stencil25_step_noalloc(float *out, const float *in, int nx, int ny, int nz, const float coeff[5],
+                                   void *stream) {
+  if (!out || !in || !coeff || nx <= 0 || ny <= 0 || nz <= 0 || (nx % portable::PS_TX) || (ny % portable::PS_TY) ||
+      !aligned16(out) || !aligned16(in) || out == in)
+    return CUDADMA_ERR_ARG;
+  const size_t padded = (size_t)(nx + 8) * (size_t)(ny + 8) * (size_t)(nz + 8);
+  if (padded > NOALLOC_MAX_FLOATS) return CUDADMA_ERR_TOO_LARGE;
+  const int sms = sm_count();
+  if (sms <= 0) { t_last_cuda_error = (int)cudaErrorNoDevice; return CUDADMA_ERR_CUDA; }
+  float *scratch = nullptr;
+  if (int r = noalloc_scratch(&scratch)) return r;
+  cudaStream_t s = (cudaStream_t)stream;
+  float *pin = scratch, *pout = scratch + NOALLOC_MAX_FLOATS;
+  /* the array still holds the previous call's field: the zero border of both copies is re-made every time */
+  CK(cudaMemsetAsync(pin, 0, padded * sizeof(float), s));
+  CK(cudaMemsetAsync(pout, 0, padded * sizeof(float), s));
+  if (int r = pad_copy(pin, const_cast<float *>(in), nx, ny, nz, 0, nz, true, s)) return r;
+  if (int e = portable::launch_stencil_padded(pout, pin, nx, ny, nz, 0, nz, coeff, 0, sms, s)) {
+    t_last_cuda_error = e;
+    return CUDADMA_ERR_CUDA;
+  }
+  ++g_launches;
+  return pad_copy(pout, out, nx, ny, nz, 0, nz, false, s);
 }
 
 int cudadma_release_workspace(void) {

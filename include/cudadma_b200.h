@@ -30,6 +30,7 @@ enum {
   CUDADMA_ERR_CUDA = -2,        /* a CUDA call failed; see cudadma_last_cuda_error() */
   CUDADMA_ERR_UNSUPPORTED = -3, /* impl not built into this library */
   CUDADMA_ERR_NOMEM = -4,       /* device or pinned memory could not be had */
+  CUDADMA_ERR_TOO_LARGE = -5,   /* cudadma_stencil25_step_noalloc: the padded grid exceeds its built-in scratch */
   CUDADMA_ERR_TIMEOUT = 1       /* a wait inside the kernel gave up; see cudadma_device_status() */
 };
 
@@ -94,6 +95,34 @@ int cudadma_stencil25_run(float *a, float *b, int nx, int ny, int nz, const floa
  * the library workspace, run this kernel there and copy the result back. */
 int cudadma_stencil25_step_padded(float *out, const float *in, int nx, int ny, int nz, int z_begin, int z_end,
                                   const float coeff[5], int z_chunk, int impl, void *stream);
+
+/* One stencil step for callers that must not allocate device memory. (No counterpart in the
+ * reference, which has no host library at all.)
+ *
+ * cudadma_stencil25_step with impl = portable keeps its two padded copies of the field in a
+ * workspace that the library obtains with cudaMalloc the first time, and again whenever a
+ * larger grid arrives. That is wrong for a solver whose framework has already taken the whole
+ * device into its own memory pool (the driver allocation then fails, or succeeds and starves
+ * the pool), and for a time-step loop that runs next to other streams, because cudaMalloc and
+ * cudaFree stall the whole device while they work. This entry point runs the same kernel with
+ * the padded copies in an array that is part of the library image instead, so it makes no
+ * cudaMalloc, no cudaFree and no other allocating call, at any time.
+ *
+ * What that costs and what to watch:
+ *   - the array is 16 MiB and every GPU that loads the library carries it until the process
+ *     exits, whether or not this function is ever called;
+ *   - the padded grid (nx + 8) * (ny + 8) * (nz + 8) may have at most 2^21 cells (for
+ *     example 120 x 112 x 120); a larger one returns CUDADMA_ERR_TOO_LARGE and touches nothing;
+ *   - all calls on a GPU share the array. Each call first re-makes the zero border it needs,
+ *     so the previous call's leftovers do no harm, but two calls whose work overlaps on the GPU
+ *     (different streams, no ordering between them) race on it: keep them on one stream or
+ *     order them with events;
+ *   - the first call on each GPU looks up the array's device address (one runtime query, with
+ *     that GPU current); make that first call before any stream capture begins.
+ * Same arguments and result as cudadma_stencil25_step(out, in, nx, ny, nz, 0, nz, coeff, 0,
+ * CUDADMA_IMPL_PORTABLE, stream): nx % 32 == 0, ny % 16 == 0, pointers 16-byte aligned, in != out. */
+int cudadma_stencil25_step_noalloc(float *out, const float *in, int nx, int ny, int nz, const float coeff[5],
+                                   void *stream);
 
 /* Host-buffer forms: the same workloads for callers that hold their data in
  * host memory. Inputs are copied to the device, the kernel runs, the result
