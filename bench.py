@@ -32,7 +32,11 @@ import torch.distributed as dist
 NX, NY, NZ = 1024, 1024, 2048          # the sharded stencil configuration
 C4 = (512, 512, 512)                   # the single-GPU stencil configuration
 BYTES_PER_POINT = 8                    # one fp32 read + one fp32 write per point and step
+# DRAM bytes per point of stencil25::tensor_kernel: dram__bytes_read + dram__bytes_write of an ncu capture
+# of the 512^3 case (1044.0 MB per launch; summary under profiles/), which grows in proportion to the points
+STENCIL_DRAM_BYTES_PER_POINT = 1044.0e6 / 512 ** 3
 L2_FLUSH_BYTES = 256 << 20
+EXCHANGE = "p2p"                       # halo exchange of this repository's arm at N > 1 (--exchange)
 
 
 def measured_peaks():
@@ -106,6 +110,9 @@ def setup_dist(n_gpus):
     torch.cuda.set_device(local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        # NCCL prints its version banner on stdout at the VERSION level; stdout carries the JSON line only
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     if world != n_gpus and rank == 0:
         print("warning: --gpus %d but WORLD_SIZE=%d; using WORLD_SIZE" % (n_gpus, world), file=sys.stderr)
@@ -320,7 +327,7 @@ def make_stencil(impl, nz_global):
     import cudadma_b200 as cd
     from cudadma_b200.sharded import ShardedStencil
     if impl == "ours":
-        return ShardedStencil(NX, NY, nz_global)
+        return ShardedStencil(NX, NY, nz_global, exchange=EXCHANGE)
     from oracle import reference as ref
 
     def step(out, inp, nx, ny, nz_total, zb, ze, coeff):
@@ -391,12 +398,14 @@ def run_stencil_job(impl, args, rank, world, local, peak, peak_kind):
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "sharded 25-point stencil, grid %dx%dx%d, 32x16 tiles + radius-4 halo, "
                                "4-plane halo exchange per step" % (NX, NY, NZ),
-                   "planes_per_gpu": NZ // world, "exchange": "torch.distributed send/recv (NCCL)" if world > 1 else "none",
+                   "planes_per_gpu": NZ // world, "exchange": ("none" if world == 1 else "torch.distributed send/recv (NCCL)" if (impl != "ours" or EXCHANGE == "nccl")
+                                else "boundary kernel stores into the neighbours' ghost planes over NVLink (CUDA IPC), flag handshake"),
                    "l2": "inputs larger than L2 (%.1f GiB per array per GPU)" % (slab_pts * 4 / 2**30),
                    "synthetic_for": "uniform[0,1) field from a seeded generator"},
         "roofline": {"bound": "hbm", "achieved": round(BYTES_PER_POINT * pts / world / per_step_ms / 1e6, 1),
                      "peak": peak, "unit": "GB/s",
-                     "frac": round(BYTES_PER_POINT * pts / world / per_step_ms / 1e6 / peak, 4), "traffic": None,
+                     "frac": round(BYTES_PER_POINT * pts / world / per_step_ms / 1e6 / peak, 4),
+                     "traffic": int(STENCIL_DRAM_BYTES_PER_POINT * pts / world) if impl == "ours" else None,
                      "peak_kind": "of " + peak_kind,
                      "kernel": "stencil25::tensor_kernel" if impl == "ours" else "portable::stencil_kernel",
                      "algorithmic_bytes_per_launch": BYTES_PER_POINT * pts // world},
@@ -446,7 +455,17 @@ def profile_case(case, reps):
     print("profile case %s: %d launches done" % (case, reps))
 
 
+def claim_stdout():
+    """Libraries underneath (NCCL's version banner, for one) write to file descriptor 1. Point it at
+    stderr for the duration of the run and return a file on the real stdout for the JSON line."""
+    sys.stdout.flush()
+    real = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+    return real
+
+
 def main():
+    json_out = claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
@@ -455,10 +474,14 @@ def main():
     ap.add_argument("--no-patterns", action="store_true", help="skip the single-GPU data-movement patterns")
     ap.add_argument("--no-weak", action="store_true", help="skip the weak-scaling companion run")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
+    ap.add_argument("--exchange", default="p2p", choices=("p2p", "nccl"),
+                    help="halo exchange at N > 1: peer-to-peer stores from the boundary kernel, or NCCL send/recv")
     ap.add_argument("--profile-case", default=None,
                     help="run only a small case of one kernel (stencil_512, sequential, strided, indirect) "
                          "--steps times, for a profiler capture")
     args = ap.parse_args()
+    global EXCHANGE
+    EXCHANGE = args.exchange
     peak, peak_kind = measured_peaks()
     if args.profile_case:
         if not torch.cuda.is_available():
@@ -479,7 +502,7 @@ def main():
             # the reference's classes were not compiled here: time the CPU restatement, rank 0 only
             if rank == 0:
                 cb = cpu_baseline_stencil()
-                print(json.dumps({
+                print(file=json_out, flush=True, *[json.dumps({
                     "impl": "reference", "metric": "stencil Gpts/s (radius-4 25-point fp32, %dx%dx%d)" % (NX, NY, NZ),
                     "value": round(cb["value"], 4), "unit": "Gpts/s", "n_gpus": world, "steps": args.steps,
                     "warmup": args.warmup, "ms_per_step": round(NX * NY * NZ / cb["value"] / 1e6, 2),
@@ -487,7 +510,7 @@ def main():
                     "data": "synthetic", "config": {"workload": "CPU restatement, " + cb["sample"]},
                     "cpu_baseline": cb,
                     "e2e": {"value": round(cb["value"], 4), "unit": "Gpts/s", "h2d_bytes_per_step": 0,
-                            "d2h_bytes_per_step": 0}}))
+                            "d2h_bytes_per_step": 0}})])
             if dist.is_initialized():
                 dist.destroy_process_group()
             return
@@ -499,7 +522,7 @@ def main():
     torch.cuda.empty_cache()
     if impl == "ours":
         # launches of this library per timed step: one kernel at N = 1, three (two boundary runs + interior) at N > 1
-        line["gpu_launches"] = args.steps * (1 if world == 1 else 3)
+        line["gpu_launches"] = args.steps * (1 if world == 1 else (5 if EXCHANGE == "p2p" else 3))
         line["launches_total_this_process"] = cd.launch_count() - before
     else:
         line["impl"] = "reference"
@@ -515,7 +538,7 @@ def main():
         if world == 1:
             line["cpu_baseline"]["patterns"] = cpu_baseline_patterns()
     if rank == 0:
-        print(json.dumps(line))
+        print(json.dumps(line), file=json_out, flush=True)
     if dist.is_initialized():
         barrier()
         dist.destroy_process_group()

@@ -30,6 +30,8 @@ SYMBOLS = [
     ("cudadma_strided_transpose", _c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.c_void_p]),
     ("cudadma_gather_scatter", _c.c_int,
      [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_int, _c.c_int, _c.c_void_p]),
+    ("cudadma_gather_scatter_tma", _c.c_int,
+     [_c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_int, _c.c_void_p]),
     ("cudadma_stencil25_step", _c.c_int,
      [_c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.POINTER(_c.c_float), _c.c_int,
       _c.c_int, _c.c_void_p]),
@@ -41,6 +43,13 @@ SYMBOLS = [
       _c.c_int, _c.c_void_p]),
     ("cudadma_stencil25_step_noalloc", _c.c_int,
      [_c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.POINTER(_c.c_float), _c.c_void_p]),
+    ("cudadma_slab_create", _c.c_int, [_c.POINTER(_c.c_void_p), _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int]),
+    ("cudadma_slab_handle_bytes", _c.c_size_t, []),
+    ("cudadma_slab_export", _c.c_int, [_c.c_void_p, _c.c_void_p]),
+    ("cudadma_slab_connect", _c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p]),
+    ("cudadma_slab_buffer", _c.c_int, [_c.c_void_p, _c.c_int, _c.POINTER(_c.c_void_p)]),
+    ("cudadma_slab_step", _c.c_int, [_c.c_void_p, _c.POINTER(_c.c_float), _c.c_void_p]),
+    ("cudadma_slab_destroy", _c.c_int, [_c.c_void_p]),
     ("cudadma_seq_copy_host", _c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_int, _c.c_int]),
     ("cudadma_strided_transpose_host", _c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int]),
     ("cudadma_gather_scatter_host", _c.c_int,
@@ -162,6 +171,16 @@ def gather_scatter(out, table, gather_idx, scatter_idx, n=None, record_bytes=32,
                                         _IMPLS[impl], _stream(stream)))
 
 
+def gather_scatter_tma(out, table, table_records, gather_idx, scatter_idx, n=None, record_bytes=32, stream=None):
+    """gather_scatter with the gather issued as TMA row gathers (four records per instruction)."""
+    _require_cuda(out, table, gather_idx, scatter_idx)
+    if n is None:
+        n = gather_idx.numel()
+    _check("cudadma_gather_scatter_tma",
+           lib().cudadma_gather_scatter_tma(_ptr(out), _ptr(table), table_records, _ptr(gather_idx),
+                                            _ptr(scatter_idx), n, record_bytes, _stream(stream)))
+
+
 def stencil25_step(out, inp, nx, ny, nz, z_begin=0, z_end=None, coeff=None, z_chunk=0, impl="native", stream=None):
     _require_cuda(out, inp)
     if z_end is None:
@@ -199,6 +218,58 @@ def stencil25_run(a, b, nx, ny, nz, steps, coeff=None, impl="native", stream=Non
            lib().cudadma_stencil25_run(_ptr(a), _ptr(b), nx, ny, nz, _coeffs(coeff), steps, _IMPLS[impl],
                                        _stream(stream)))
     return a if steps % 2 == 0 else b
+
+
+# ---- slabs of the z-sharded stencil with peer-to-peer halo pushes ----
+
+class Slab:
+    """This rank's planes of a z-sharded grid, in two arrays the library allocates so that the
+    z-neighbour processes can map them (CUDA IPC) and push their boundary planes into the ghost
+    planes. export() bytes go to both neighbours by any means; connect() takes theirs."""
+
+    def __init__(self, nx, ny, nzl, has_lower, has_upper):
+        self.nx, self.ny, self.nzl = nx, ny, nzl
+        h = ctypes.c_void_p()
+        _check("cudadma_slab_create", lib().cudadma_slab_create(ctypes.byref(h), nx, ny, nzl, int(has_lower),
+                                                                int(has_upper)))
+        self._h = h
+
+    def export(self):
+        buf = ctypes.create_string_buffer(lib().cudadma_slab_handle_bytes())
+        _check("cudadma_slab_export", lib().cudadma_slab_export(self._h, buf))
+        return buf.raw
+
+    def connect(self, lower, upper):
+        _check("cudadma_slab_connect", lib().cudadma_slab_connect(self._h, lower, upper))
+
+    def buffer_address(self, which=0):
+        p = ctypes.c_void_p()
+        _check("cudadma_slab_buffer", lib().cudadma_slab_buffer(self._h, which, ctypes.byref(p)))
+        return p.value
+
+    def tensor(self, which=0):
+        """The array as a flat float32 torch tensor over the library's memory (no copy)."""
+        import torch
+        n = (self.nzl + 8) * self.ny * self.nx
+
+        class _Raw:
+            __cuda_array_interface__ = {"shape": (n,), "typestr": "<f4", "data": (self.buffer_address(which), False),
+                                        "version": 2}
+        return torch.as_tensor(_Raw(), device="cuda")
+
+    def step(self, coeff=None, stream=None):
+        _check("cudadma_slab_step", lib().cudadma_slab_step(self._h, _coeffs(coeff), _stream(stream)))
+
+    def destroy(self):
+        if self._h is not None:
+            lib().cudadma_slab_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass
 
 
 # ---- host-buffer forms (numpy arrays or pinned CPU tensors) ----

@@ -9,6 +9,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <stdlib.h>
 #include <string.h>
 
 #include <atomic>
@@ -151,6 +152,41 @@ int finish_status(cudaStream_t s) {
   unsigned int w = 0;
   CK(cudadma_b200::read_status(&w, s));
   return w ? CUDADMA_ERR_TIMEOUT : CUDADMA_OK;
+}
+
+/* Launch of the tensor-map stencil kernel on output planes [z_begin, z_end); peer_out (may be
+ * null) is a second destination for every output, at the same plane numbers. */
+int launch_stencil_native(float *out, float *peer_out, const float *in, int nx, int ny, int nz, int z_begin, int z_end,
+                          const float coeff[5], int z_chunk, cudaStream_t s) {
+  const int sms = sm_count();
+  if (sms <= 0) { t_last_cuda_error = (int)cudaErrorNoDevice; return CUDADMA_ERR_CUDA; }
+  stencil25::Coeffs k;
+  for (int i = 0; i < 5; ++i) k.c[i] = coeff[i];
+  const int tiles_x = (nx + stencil25::TILE_X - 1) / stencil25::TILE_X;
+  const int tiles_y = (ny + stencil25::TILE_Y - 1) / stencil25::TILE_Y;
+  const int depth = z_end - z_begin;
+  if (z_chunk <= 0) {
+    /* enough CTAs for a few waves over the SMs, but runs of at least 32 planes so that the
+     * eight lead-in/lead-out planes of a run stay a small share of its loads */
+    const long long tiles = (long long)tiles_x * tiles_y;
+    const long long want = (long long)STENCIL_CTAS_TARGET * sms;
+    long long chunks = (want + tiles - 1) / tiles;
+    if (chunks < 1) chunks = 1;
+    z_chunk = (int)((depth + chunks - 1) / chunks);
+    if (z_chunk < 32) z_chunk = 32;
+    if (z_chunk > depth) z_chunk = depth;
+  }
+  const int zc = (depth + z_chunk - 1) / z_chunk;
+  if (zc > 65535 || tiles_y > 65535) return CUDADMA_ERR_ARG;
+  CUtensorMap map;
+  const cuuint64_t dims[3] = {(cuuint64_t)nx, (cuuint64_t)ny, (cuuint64_t)nz};
+  const cuuint64_t strides[2] = {(cuuint64_t)nx * 4, (cuuint64_t)nx * ny * 4};
+  const cuuint32_t box[3] = {stencil25::WIN_X, stencil25::WIN_Y, 1};
+  if (int r = make_map_f32(&map, in, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, STENCIL25_L2PROMO)) return r;
+  dim3 grid(tiles_x, tiles_y, zc);
+  stencil25::tensor_kernel<<<grid, stencil25::COMPUTE_THREADS + stencil25::DMA_THREADS, stencil25::SMEM_BYTES, s>>>(
+      map, out, peer_out, nx, ny, z_begin, z_end, z_chunk, k);
+  return launched();
 }
 
 /* copy between a plain nx x ny x nz array and one padded by four cells on every side */
@@ -298,6 +334,7 @@ int cudadma_strided_transpose(float *dst, const float *src, int rows, int cols, 
 int cudadma_gather_scatter(void *out, const void *table, const int32_t *gather_idx, const int32_t *scatter_idx,
                            size_t n, int record_bytes, int impl, void *stream) {
   using namespace cudadma_b200::kernels;
+
   if (!out || !table || !gather_idx || !scatter_idx || record_bytes != 32 || (n % 128) || !aligned16(out) ||
       !aligned16(table) || !aligned16(gather_idx) || !aligned16(scatter_idx))
     return CUDADMA_ERR_ARG;
@@ -329,6 +366,37 @@ int cudadma_gather_scatter(void *out, const void *table, const int32_t *gather_i
   return CUDADMA_ERR_UNSUPPORTED;
 }
 
+int cudadma_gather_scatter_tma(void *out, const void *table, size_t table_records, const int32_t *gather_idx,
+                               const int32_t *scatter_idx, size_t n, int record_bytes, void *stream) {
+  using namespace cudadma_b200::kernels;
+  if (!out || !table || !gather_idx || !scatter_idx || record_bytes != 32 || (n % 128) || table_records == 0 ||
+      table_records > 0x7fffffffull || !aligned16(out) || !aligned16(table) || !aligned16(gather_idx) ||
+      !aligned16(scatter_idx))
+    return CUDADMA_ERR_ARG;
+  if (n == 0) return CUDADMA_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int sms = sm_count();
+  if (sms <= 0) { t_last_cuda_error = (int)cudaErrorNoDevice; return CUDADMA_ERR_CUDA; }
+  const long long nbuf = (long long)(n / 128);
+  /* the table as a 2-D tensor [records][8 floats] whose box is one record: each TMA instruction
+   * of the gather object names four records */
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {8, (cuuint64_t)table_records};
+  const cuuint64_t strides[1] = {32};
+  const cuuint32_t box[2] = {8, 1};
+  if (int r = make_map_f32(&map, table, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE,
+                           CU_TENSOR_MAP_L2_PROMOTION_NONE))
+    return r;
+  constexpr int STAGES = GS_STAGES;
+  constexpr int SMEM = STAGES * 128 * 32;
+  auto k = gather4_scatter_kernel<32, 128, STAGES>;
+  if (int r = allow_smem(k, SMEM)) return r;
+  const long long want = (long long)GS_CTAS_PER_SM * sms;
+  const int grid = (int)(nbuf < want ? nbuf : want);
+  k<<<grid, GS_THREADS, SMEM, s>>>(map, static_cast<char *>(out), gather_idx, scatter_idx, nbuf);
+  return launched();
+}
+
 int cudadma_stencil25_step(float *out, const float *in, int nx, int ny, int nz, int z_begin, int z_end,
                            const float coeff[5], int z_chunk, int impl, void *stream) {
   if (!out || !in || !coeff || nx <= 0 || ny <= 0 || nz <= 0 || (nx & 3) || z_begin < 0 || z_end > nz ||
@@ -340,44 +408,8 @@ int cudadma_stencil25_step(float *out, const float *in, int nx, int ny, int nz, 
   if (sms <= 0) { t_last_cuda_error = (int)cudaErrorNoDevice; return CUDADMA_ERR_CUDA; }
   if (impl == CUDADMA_IMPL_PORTABLE)
     return portable_stencil(const_cast<float *>(in), out, nx, ny, nz, z_begin, z_end, coeff, 1, z_chunk, s);
-  stencil25::Coeffs k;
-  for (int i = 0; i < 5; ++i) k.c[i] = coeff[i];
-  const int tiles_x = (nx + stencil25::TILE_X - 1) / stencil25::TILE_X;
-  const int tiles_y = (ny + stencil25::TILE_Y - 1) / stencil25::TILE_Y;
-  const int depth = z_end - z_begin;
-  if (z_chunk <= 0) {
-    /* enough CTAs for a few waves over the SMs, but runs of at least 32 planes so that the
-     * eight lead-in/lead-out planes of a run stay a small share of its loads */
-    const long long tiles = (long long)tiles_x * tiles_y;
-    const long long want = (long long)STENCIL_CTAS_TARGET * sms;
-    long long chunks = (want + tiles - 1) / tiles;
-    if (chunks < 1) chunks = 1;
-    z_chunk = (int)((depth + chunks - 1) / chunks);
-    if (z_chunk < 32) z_chunk = 32;
-    if (z_chunk > depth) z_chunk = depth;
-  }
-  const int zc = (depth + z_chunk - 1) / z_chunk;
-  if (zc > 65535 || tiles_y > 65535) return CUDADMA_ERR_ARG;
-  if (impl == CUDADMA_IMPL_NATIVE) {
-    CUtensorMap map;
-    const cuuint64_t dims[3] = {(cuuint64_t)nx, (cuuint64_t)ny, (cuuint64_t)nz};
-    const cuuint64_t strides[2] = {(cuuint64_t)nx * 4, (cuuint64_t)nx * ny * 4};
-#ifdef STENCIL25_DIAG_INTERIOR_ONLY
-    const cuuint32_t box[3] = {stencil25::TILE_X, stencil25::TILE_Y, 1};
-#else
-    const cuuint32_t box[3] = {stencil25::WIN_X, stencil25::WIN_Y, 1};
-#endif
-    if (int r = make_map_f32(&map, in, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, STENCIL25_L2PROMO)) return r;
-    dim3 grid(tiles_x, tiles_y, zc);
-#ifdef STENCIL25_CARVEOUT
-    CK(cudaFuncSetAttribute(stencil25::tensor_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
-                            STENCIL25_CARVEOUT));
-#endif
-    stencil25::tensor_kernel<<<grid, stencil25::COMPUTE_THREADS + stencil25::DMA_THREADS, stencil25::SMEM_BYTES, s>>>(
-        map, out, nx, ny, z_begin, z_end, z_chunk, k);
-    return launched();
-  }
-  return CUDADMA_ERR_UNSUPPORTED;
+  if (impl != CUDADMA_IMPL_NATIVE) return CUDADMA_ERR_UNSUPPORTED;
+  return launch_stencil_native(out, nullptr, in, nx, ny, nz, z_begin, z_end, coeff, z_chunk, s);
 }
 
 int cudadma_stencil25_run(float *a, float *b, int nx, int ny, int nz, const float coeff[5], int steps, int impl,
@@ -411,6 +443,185 @@ int cudadma_stencil25_step_padded(float *out, const float *in, int nx, int ny, i
     return CUDADMA_ERR_CUDA;
   }
   ++g_launches;
+  return CUDADMA_OK;
+}
+
+/* ---- z-sharded stencil with halo planes pushed straight into the neighbour GPUs ---- */
+
+}  /* extern "C" */
+
+namespace {
+
+struct SlabHandles {            /* what a rank publishes to its z-neighbours */
+  cudaIpcMemHandle_t buf[2];
+  cudaIpcMemHandle_t flags;
+  int nzl;
+};
+
+struct Slab {
+  int nx, ny, nzl;
+  bool has_lo, has_hi;
+  float *buf[2];                /* (nzl + 8) planes each: four ghost planes, the owned planes, four ghost planes */
+  unsigned int *flags;          /* [0] steps finished by the lower neighbour, [1] by the upper one (they write) */
+  float *lo_buf[2], *hi_buf[2]; /* the neighbours' arrays, mapped into this process */
+  unsigned int *lo_flags, *hi_flags;
+  int nzl_lo;                   /* planes the lower neighbour owns */
+  int cur;                      /* buf[cur] holds the current field */
+  unsigned int step;            /* steps finished */
+};
+
+constexpr long long SLAB_WAIT_LIMIT_CYCLES = 1ll << 32; /* about two seconds */
+
+/* One thread waits until both neighbours have finished `need` steps. Their flag words live in
+ * this GPU's memory and are written from the other GPUs, hence the system-scope loads. The wait
+ * is bounded: on expiry it records a code in the status word and lets the step go on. */
+__global__ void slab_wait_kernel(const unsigned int *flag_lo, const unsigned int *flag_hi, const unsigned int need) {
+  const unsigned int *flags[2] = {flag_lo, flag_hi};
+  for (int i = 0; i < 2; ++i) {
+    if (!flags[i]) continue;
+    const long long t0 = clock64();
+    for (;;) {
+      unsigned int v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags[i]) : "memory");
+      if (v >= need) break;
+      if (clock64() - t0 > SLAB_WAIT_LIMIT_CYCLES) {
+        atomicCAS(&cudadma_b200::g_status_word, 0u, 0x80000000u | 0xE000u | (unsigned)i);
+        break;
+      }
+      __nanosleep(200);
+    }
+  }
+}
+
+/* Tells both neighbours that this rank has finished `value` steps: everything the earlier kernels
+ * of the stream wrote (its own planes and the copies pushed into the neighbours' ghost planes)
+ * is ordered before the flag by the system-scope fence and release store. */
+__global__ void slab_signal_kernel(unsigned int *peer_lo, unsigned int *peer_hi, const unsigned int value) {
+  __threadfence_system();
+  if (peer_lo) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peer_lo), "r"(value) : "memory");
+  if (peer_hi) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peer_hi), "r"(value) : "memory");
+}
+
+}  // namespace
+
+extern "C" {
+
+int cudadma_slab_create(void **out, int nx, int ny, int nzl, int has_lower, int has_upper) {
+  if (!out || nx <= 0 || ny <= 0 || (nx & 3) || nzl <= 0 || ((has_lower || has_upper) && nzl < 8)) return CUDADMA_ERR_ARG;
+  Slab *sl = new Slab();
+  sl->nx = nx; sl->ny = ny; sl->nzl = nzl;
+  sl->has_lo = has_lower != 0; sl->has_hi = has_upper != 0;
+  const size_t bytes = (size_t)nx * ny * (nzl + 8) * sizeof(float);
+  cudaError_t e = cudaMalloc(&sl->buf[0], bytes);
+  if (e == cudaSuccess) e = cudaMalloc(&sl->buf[1], bytes);
+  if (e == cudaSuccess) e = cudaMalloc(&sl->flags, 256);
+  if (e == cudaSuccess) e = cudaMemset(sl->buf[0], 0, bytes);
+  if (e == cudaSuccess) e = cudaMemset(sl->buf[1], 0, bytes);
+  if (e == cudaSuccess) e = cudaMemset(sl->flags, 0, 256);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) {
+    t_last_cuda_error = (int)e;
+    cudaFree(sl->buf[0]); cudaFree(sl->buf[1]); cudaFree(sl->flags);
+    delete sl;
+    cudaGetLastError();
+    return e == cudaErrorMemoryAllocation ? CUDADMA_ERR_NOMEM : CUDADMA_ERR_CUDA;
+  }
+  *out = sl;
+  return CUDADMA_OK;
+}
+
+size_t cudadma_slab_handle_bytes(void) { return sizeof(SlabHandles); }
+
+int cudadma_slab_export(void *slab, void *handles) {
+  Slab *sl = static_cast<Slab *>(slab);
+  if (!sl || !handles) return CUDADMA_ERR_ARG;
+  SlabHandles h;
+  memset(&h, 0, sizeof(h));
+  CK(cudaIpcGetMemHandle(&h.buf[0], sl->buf[0]));
+  CK(cudaIpcGetMemHandle(&h.buf[1], sl->buf[1]));
+  CK(cudaIpcGetMemHandle(&h.flags, sl->flags));
+  h.nzl = sl->nzl;
+  memcpy(handles, &h, sizeof(h));
+  return CUDADMA_OK;
+}
+
+int cudadma_slab_connect(void *slab, const void *lower_handles, const void *upper_handles) {
+  Slab *sl = static_cast<Slab *>(slab);
+  if (!sl || (sl->has_lo && !lower_handles) || (sl->has_hi && !upper_handles)) return CUDADMA_ERR_ARG;
+  if (sl->has_lo) {
+    SlabHandles h;
+    memcpy(&h, lower_handles, sizeof(h));
+    CK(cudaIpcOpenMemHandle((void **)&sl->lo_buf[0], h.buf[0], cudaIpcMemLazyEnablePeerAccess));
+    CK(cudaIpcOpenMemHandle((void **)&sl->lo_buf[1], h.buf[1], cudaIpcMemLazyEnablePeerAccess));
+    CK(cudaIpcOpenMemHandle((void **)&sl->lo_flags, h.flags, cudaIpcMemLazyEnablePeerAccess));
+    sl->nzl_lo = h.nzl;
+  }
+  if (sl->has_hi) {
+    SlabHandles h;
+    memcpy(&h, upper_handles, sizeof(h));
+    CK(cudaIpcOpenMemHandle((void **)&sl->hi_buf[0], h.buf[0], cudaIpcMemLazyEnablePeerAccess));
+    CK(cudaIpcOpenMemHandle((void **)&sl->hi_buf[1], h.buf[1], cudaIpcMemLazyEnablePeerAccess));
+    CK(cudaIpcOpenMemHandle((void **)&sl->hi_flags, h.flags, cudaIpcMemLazyEnablePeerAccess));
+  }
+  return CUDADMA_OK;
+}
+
+int cudadma_slab_buffer(void *slab, int which, float **ptr) {
+  Slab *sl = static_cast<Slab *>(slab);
+  if (!sl || !ptr || which < 0 || which > 1) return CUDADMA_ERR_ARG;
+  *ptr = sl->buf[which ? (sl->cur ^ 1) : sl->cur];
+  return CUDADMA_OK;
+}
+
+int cudadma_slab_step(void *slab, const float coeff[5], void *stream) {
+  Slab *sl = static_cast<Slab *>(slab);
+  if (!sl || !coeff) return CUDADMA_ERR_ARG;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int nx = sl->nx, ny = sl->ny, nzl = sl->nzl, nzt = nzl + 8;
+  const long long pz = (long long)nx * ny;
+  float *cur = sl->buf[sl->cur], *nxt = sl->buf[sl->cur ^ 1];
+  const int first = 4, last = 4 + nzl;
+  int lo_end = first, hi_begin = last;
+  if (sl->has_lo || sl->has_hi) {
+    /* neighbours must have finished the previous step: their copies of it are in this rank's ghost
+     * planes, and they no longer read the ghost planes this step is about to overwrite */
+    slab_wait_kernel<<<1, 1, 0, s>>>(sl->has_lo ? sl->flags + 0 : nullptr, sl->has_hi ? sl->flags + 1 : nullptr,
+                                     sl->step);
+    if (int r = launched()) return r;
+  }
+  if (sl->has_lo) {
+    lo_end = first + 4;
+    /* plane z of this rank is plane z + nzl_lo of the lower neighbour (its upper ghost planes) */
+    float *peer = sl->lo_buf[sl->cur ^ 1] + (long long)sl->nzl_lo * pz;
+    if (int r = launch_stencil_native(nxt, peer, cur, nx, ny, nzt, first, lo_end, coeff, 0, s)) return r;
+  }
+  if (sl->has_hi) {
+    hi_begin = last - 4;
+    /* plane z of this rank is plane z - nzl of the upper neighbour (its lower ghost planes) */
+    float *peer = sl->hi_buf[sl->cur ^ 1] - (long long)nzl * pz;
+    if (int r = launch_stencil_native(nxt, peer, cur, nx, ny, nzt, hi_begin, last, coeff, 0, s)) return r;
+  }
+  if (lo_end < hi_begin)
+    if (int r = launch_stencil_native(nxt, nullptr, cur, nx, ny, nzt, lo_end, hi_begin, coeff, 0, s)) return r;
+  if (sl->has_lo || sl->has_hi) {
+    slab_signal_kernel<<<1, 1, 0, s>>>(sl->has_lo ? sl->lo_flags + 1 : nullptr, sl->has_hi ? sl->hi_flags + 0 : nullptr,
+                                       sl->step + 1);
+    if (int r = launched()) return r;
+  }
+  sl->cur ^= 1;
+  sl->step += 1;
+  return CUDADMA_OK;
+}
+
+int cudadma_slab_destroy(void *slab) {
+  Slab *sl = static_cast<Slab *>(slab);
+  if (!sl) return CUDADMA_OK;
+  cudaDeviceSynchronize();
+  if (sl->has_lo) { cudaIpcCloseMemHandle(sl->lo_buf[0]); cudaIpcCloseMemHandle(sl->lo_buf[1]); cudaIpcCloseMemHandle(sl->lo_flags); }
+  if (sl->has_hi) { cudaIpcCloseMemHandle(sl->hi_buf[0]); cudaIpcCloseMemHandle(sl->hi_buf[1]); cudaIpcCloseMemHandle(sl->hi_flags); }
+  cudaFree(sl->buf[0]); cudaFree(sl->buf[1]); cudaFree(sl->flags);
+  delete sl;
+  cudaGetLastError();
   return CUDADMA_OK;
 }
 

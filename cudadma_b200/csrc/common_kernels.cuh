@@ -25,6 +25,42 @@ struct StageRing<T, FIRST_ID, std::integer_sequence<int, I...>> {
 template <typename T, int STAGES, int FIRST_ID = 0>
 using Ring = StageRing<T, FIRST_ID, std::make_integer_sequence<int, STAGES>>;
 
+/* The bridging warp of the gather + scatter kernels: buffer full (gather done) -> start its
+ * scatter; LAG buffers later, once that scatter has read the buffer, hand it back to the gather
+ * object. Every arrival made here is matched by a wait on the other side (named barriers must
+ * not be left with arrivals nobody waits for), hence the guards and the drain at the end. */
+template <int STAGES, typename GRING, typename SRING>
+__device__ __forceinline__ void bridge_gather_to_scatter(GRING &g, SRING &sc, const long long nbuffers,
+                                                         const long long stride) {
+  static_assert(STAGES >= 2, "the bridge needs at least two buffers");
+  constexpr int LAG = STAGES / 2;
+#pragma unroll
+  for (int s = 0; s < STAGES; ++s)
+    if (blockIdx.x + s * stride < nbuffers) g.stage[s].start_async_dma();
+  bool more = true;
+  long long done = 0;   /* buffers of this CTA handed to a scatter object so far */
+  unsigned pending = 0; /* stages whose scatter has been started and not yet waited for */
+  for (long long b0 = blockIdx.x; more; b0 += stride * STAGES) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+      const long long b = b0 + s * stride;
+      if (b >= nbuffers) { more = false; break; }
+      g.stage[s].wait_for_dma_finish();
+      sc.stage[s].start_async_dma();
+      pending |= 1u << s;
+      ++done;
+      if (done > LAG) {
+        sc.stage[(s + STAGES - LAG) % STAGES].wait_for_dma_finish();
+        pending &= ~(1u << ((s + STAGES - LAG) % STAGES));
+        if (b + (STAGES - LAG) * stride < nbuffers) g.stage[(s + STAGES - LAG) % STAGES].start_async_dma();
+      }
+    }
+  }
+#pragma unroll
+  for (int s = 0; s < STAGES; ++s)
+    if ((pending >> s) & 1u) sc.stage[s].wait_for_dma_finish();
+}
+
 /* ------------------------------------------------------------------------ */
 /* Indirect: buffers of RECORDS records of RECORD_BYTES bytes. A gather       */
 /* object fills a shared buffer from table rows gather_idx[..], a scatter     */
@@ -66,36 +102,7 @@ gather_scatter_kernel(char *__restrict__ out, const char *__restrict__ table, co
       }
     }
   } else {
-    /* bridge: buffer full (gather done) -> start its scatter; LAG buffers later, once that
-     * scatter has read the buffer, hand it back to the gather object. Every arrival made
-     * here is matched by a wait on the other side (named barriers must not be left with
-     * arrivals nobody waits for), hence the guards and the drain at the end. */
-    constexpr int LAG = (STAGES > 1) ? STAGES / 2 : 1;
-#pragma unroll
-    for (int s = 0; s < STAGES; ++s)
-      if (blockIdx.x + s * stride < nbuffers) g.stage[s].start_async_dma();
-    bool more = true;
-    long long done = 0;   /* buffers of this CTA handed to a scatter object so far */
-    unsigned pending = 0; /* stages whose scatter has been started and not yet waited for */
-    for (long long b0 = blockIdx.x; more; b0 += stride * STAGES) {
-#pragma unroll
-      for (int s = 0; s < STAGES; ++s) {
-        const long long b = b0 + s * stride;
-        if (b >= nbuffers) { more = false; break; }
-        g.stage[s].wait_for_dma_finish();
-        sc.stage[s].start_async_dma();
-        pending |= 1u << s;
-        ++done;
-        if (done > LAG) {
-          sc.stage[(s + STAGES - LAG) % STAGES].wait_for_dma_finish();
-          pending &= ~(1u << ((s + STAGES - LAG) % STAGES));
-          if (b + (STAGES - LAG) * stride < nbuffers) g.stage[(s + STAGES - LAG) % STAGES].start_async_dma();
-        }
-      }
-    }
-#pragma unroll
-    for (int s = 0; s < STAGES; ++s)
-      if ((pending >> s) & 1u) sc.stage[s].wait_for_dma_finish();
+    bridge_gather_to_scatter<STAGES>(g, sc, nbuffers, stride);
   }
 }
 

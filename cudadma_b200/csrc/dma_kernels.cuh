@@ -182,6 +182,46 @@ transpose_kernel(const __grid_constant__ CUtensorMap in_map, float *__restrict__
   }
 }
 
+/* ------------------------------------------------------------------------ */
+/* Indirect with TMA row gathers: the gather object fetches four table records */
+/* per cp.async.bulk.tensor ... tile::gather4 instruction through a tensor map  */
+/* of the table; bridge and scatter sides are those of gather_scatter_kernel.   */
+/* ------------------------------------------------------------------------ */
+template <int RECORD_BYTES, int RECORDS, int STAGES>
+__global__ void __launch_bounds__(GS_THREADS)
+gather4_scatter_kernel(const __grid_constant__ CUtensorMap table_map, char *__restrict__ out,
+                       const int *__restrict__ gather_idx, const int *__restrict__ scatter_idx,
+                       const long long nbuffers) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  constexpr int BUF = RECORD_BYTES * RECORDS;
+  typedef CudaDMAIndirect<true, true, 16, 64, RECORD_BYTES, GS_GATHER_THREADS, RECORDS> Gather;
+  typedef CudaDMAIndirect<false, true, 16, 64, RECORD_BYTES, GS_SCATTER_THREADS, RECORDS> Scatter;
+  Ring<Gather, STAGES, 0> g(GS_BRIDGE_THREADS, GS_BRIDGE_THREADS);
+  Ring<Scatter, STAGES, STAGES> sc(GS_BRIDGE_THREADS, GS_BRIDGE_THREADS + GS_GATHER_THREADS);
+  const long long stride = gridDim.x;
+  if (g.stage[0].owns_this_thread()) {
+    for (long long b0 = blockIdx.x;; b0 += stride * STAGES) {
+#pragma unroll
+      for (int s = 0; s < STAGES; ++s) {
+        const long long b = b0 + s * stride;
+        if (b >= nbuffers) return;
+        g.stage[s].execute_dma_gather4(&table_map, gather_idx + b * RECORDS, smem + s * BUF);
+      }
+    }
+  } else if (sc.stage[0].owns_this_thread()) {
+    for (long long b0 = blockIdx.x;; b0 += stride * STAGES) {
+#pragma unroll
+      for (int s = 0; s < STAGES; ++s) {
+        const long long b = b0 + s * stride;
+        if (b >= nbuffers) return;
+        sc.stage[s].execute_dma(scatter_idx + b * RECORDS, smem + s * BUF, out);
+      }
+    }
+  } else {
+    bridge_gather_to_scatter<STAGES>(g, sc, nbuffers, stride);
+  }
+}
+
 }  // namespace kernels
 }  // namespace cudadma_b200
 

@@ -133,7 +133,10 @@ __device__ __forceinline__ void fold_plane(const float *__restrict__ win, float2
 /* in_map: 3-D tensor map over the nx x ny x nz input (x fastest), box 40 x 24 x 1.
  * Output planes [z_begin, z_end) are produced, blockIdx.z taking z_chunk of them;
  * input planes outside [0, nz) read as zero. Planes are numbered kp = 0 .. depth + 7
- * from (first output plane - 4); output plane kp - 8 is stored at step kp. */
+ * from (first output plane - 4); output plane kp - 8 is stored at step kp.
+ * peer_out, when not null, receives a second copy of every output at the same plane
+ * index: the sharded driver points it into a z-neighbour GPU's ghost planes (plain stores
+ * over NVLink), shifted so that this rank's plane numbers land on the neighbour's. */
 #if defined(STENCIL25_MAXNREG)
 __global__ void __maxnreg__(STENCIL25_MAXNREG)
 #elif defined(STENCIL25_MIN_BLOCKS)
@@ -141,16 +144,11 @@ __global__ void __launch_bounds__(COMPUTE_THREADS + DMA_THREADS, STENCIL25_MIN_B
 #else
 __global__ void __launch_bounds__(COMPUTE_THREADS + DMA_THREADS)
 #endif
-tensor_kernel(const __grid_constant__ CUtensorMap in_map, float *__restrict__ out, const int nx, const int ny,
-              const int z_begin, const int z_end, const int z_chunk, const Coeffs k) {
+tensor_kernel(const __grid_constant__ CUtensorMap in_map, float *__restrict__ out, float *__restrict__ peer_out,
+              const int nx, const int ny, const int z_begin, const int z_end, const int z_chunk, const Coeffs k) {
   extern __shared__ __align__(128) unsigned char smem[];
   typedef CudaDMAHalo<float, R, true, 16> Halo;
-#ifdef STENCIL25_DIAG_INTERIOR_ONLY
-  cudadma_b200::kernels::Ring<Halo, STAGES> ring(DMA_THREADS, COMPUTE_THREADS, COMPUTE_THREADS, TILE_X - 2 * R,
-                                                 TILE_Y - 2 * R, nx);
-#else
   cudadma_b200::kernels::Ring<Halo, STAGES> ring(DMA_THREADS, COMPUTE_THREADS, COMPUTE_THREADS, TILE_X, TILE_Y, nx);
-#endif
   const int x0 = blockIdx.x * TILE_X, y0 = blockIdx.y * TILE_Y;
   const int z0 = z_begin + blockIdx.z * z_chunk;
   const int depth = (z_end - z0 < z_chunk) ? (z_end - z0) : z_chunk;
@@ -160,22 +158,15 @@ tensor_kernel(const __grid_constant__ CUtensorMap in_map, float *__restrict__ ou
 #pragma unroll
       for (int s = 0; s < STAGES; ++s) {
         if (k0 + s >= nplanes) return;
-#ifdef STENCIL25_DIAG_INTERIOR_ONLY
-        ring.stage[s].execute_dma_tile(&in_map, x0 + R, y0 + R, z0 - R + k0 + s, smem + s * PLANE_BYTES);
-#else
-#ifdef STENCIL25_DIAG_NO_LOAD
-        ring.stage[s].wait_for_dma_start();
-        ring.stage[s].finish_async_dma();
-#else
         ring.stage[s].execute_dma_tile(&in_map, x0, y0, z0 - R + k0 + s, smem + s * PLANE_BYTES);
-#endif
-#endif
       }
     }
   } else {
     const int tx = threadIdx.x & 7, ty = threadIdx.x >> 3;
     const long long py = nx, pz = (long long)nx * ny;
-    float *o = out + (long long)z0 * pz + (long long)(y0 + 2 * ty) * py + x0 + 4 * tx;
+    const long long cell0 = (long long)z0 * pz + (long long)(y0 + 2 * ty) * py + x0 + 4 * tx;
+    float *o = out + cell0;
+    float *po = peer_out ? peer_out + cell0 : nullptr;
     const bool row0_ok = (x0 + 4 * tx < nx) && (y0 + 2 * ty < ny);
     const bool row1_ok = (x0 + 4 * tx < nx) && (y0 + 2 * ty + 1 < ny);
     const int win_off = (2 * ty + R) * WIN_X + 4 * tx + R;
@@ -193,28 +184,20 @@ tensor_kernel(const __grid_constant__ CUtensorMap in_map, float *__restrict__ ou
             if (kp < nplanes) {
               ring.stage[kk % STAGES].wait_for_dma_finish();
               const float *win = reinterpret_cast<const float *>(smem + (kk % STAGES) * PLANE_BYTES) + win_off;
-#ifdef STENCIL25_DIAG_NO_XY
-              fold_plane<kk>(win, acc, c2, false);
-#else
               fold_plane<kk>(win, acc, c2, kp >= R && kp < depth + R);
-#endif
               ring.stage[kk % STAGES].start_async_dma();
               if (kp >= 2 * R) {
                 /* output plane kp - 8 of this CTA is complete: it sits in slot (kk - 4) mod 9 */
                 const float2(&r)[2][2] = acc[(kk + SLOTS - R) % SLOTS];
-                float *oz = o + (long long)(kp - 2 * R) * pz;
-#ifdef STENCIL25_DIAG_NO_STORE
-                if (row0_ok && r[0][0].x == 123.456f)
-#else
-                if (row0_ok)
-#endif
-                  *reinterpret_cast<float4 *>(oz) = make_float4(r[0][0].x, r[0][0].y, r[0][1].x, r[0][1].y);
-#ifdef STENCIL25_DIAG_NO_STORE
-                if (row1_ok && r[1][0].x == 123.456f)
-#else
-                if (row1_ok)
-#endif
-                  *reinterpret_cast<float4 *>(oz + py) = make_float4(r[1][0].x, r[1][0].y, r[1][1].x, r[1][1].y);
+                const long long plane = (long long)(kp - 2 * R) * pz;
+                const float4 v0 = make_float4(r[0][0].x, r[0][0].y, r[0][1].x, r[0][1].y);
+                const float4 v1 = make_float4(r[1][0].x, r[1][0].y, r[1][1].x, r[1][1].y);
+                if (row0_ok) *reinterpret_cast<float4 *>(o + plane) = v0;
+                if (row1_ok) *reinterpret_cast<float4 *>(o + plane + py) = v1;
+                if (po) {
+                  if (row0_ok) *reinterpret_cast<float4 *>(po + plane) = v0;
+                  if (row1_ok) *reinterpret_cast<float4 *>(po + plane + py) = v1;
+                }
               }
             }
           },

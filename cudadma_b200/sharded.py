@@ -9,12 +9,17 @@ the four boundary planes of a side are one contiguous block. Ghost planes
 beyond the ends of the global grid stay zero, which is the stencil's
 out-of-grid rule.
 
-One step:
+One step, exchange = "nccl":
   1. the first and last four owned planes are computed first;
   2. they are sent to the z-neighbours' ghost planes (torch.distributed
      send/recv: NCCL over NVLink on GPUs) on a side stream;
   3. the remaining interior planes are computed meanwhile on the main stream;
   4. the main stream joins the exchange, buffers swap.
+One step, exchange = "p2p" (CUDA devices only): the boundary kernel itself stores
+every result twice, into this rank's array and into the neighbour's ghost planes
+over NVLink (the arrays are shared between the processes with CUDA IPC), and a
+flag word per neighbour says how many steps each side has finished; see
+cudadma_slab_step in include/cudadma_b200.h. No collective library on the step.
 Every plane is computed by the same kernel with the same arithmetic whatever
 the sharding, so an N-rank run reproduces the 1-rank field bit for bit.
 """
@@ -43,7 +48,7 @@ class ShardedStencil:
     through the C ABI (there is no CPU path in the product; tests of the host logic on
     CPU ranks pass their own step function)."""
 
-    def __init__(self, nx, ny, nz, coeff=None, device=None, group=None, step_fn=None, pad_xy=0):
+    def __init__(self, nx, ny, nz, coeff=None, device=None, group=None, step_fn=None, pad_xy=0, exchange="nccl"):
         """pad_xy: zero cells kept around every plane in x and y (0 for the tensor-map kernel, which
         needs no border; 4 for kernels that read a padded array). The step function sees the padded
         planes: nx + 2 * pad_xy by ny + 2 * pad_xy."""
@@ -69,8 +74,21 @@ class ShardedStencil:
         self.px, self.py = nx + 2 * pad_xy, ny + 2 * pad_xy
         plane = self.px * self.py
         self.plane = plane
-        self.cur = torch.zeros((self.nzl + 2 * R) * plane, dtype=torch.float32, device=self.device)
-        self.nxt = torch.zeros_like(self.cur)
+        if exchange not in ("nccl", "p2p"):
+            raise ValueError("exchange is 'nccl' or 'p2p'")
+        self.slab = None
+        if exchange == "p2p" and self.world > 1:
+            if not self.on_cuda or step_fn is not _cuda_step or pad_xy != 0:
+                raise ValueError("the peer-to-peer exchange belongs to the CUDA kernel of this library")
+            self.slab = capi.Slab(nx, ny, self.nzl, self.rank > 0, self.rank < self.world - 1)
+            blobs = [None] * self.world
+            dist.all_gather_object(blobs, self.slab.export(), group=group)
+            self.slab.connect(blobs[self.rank - 1] if self.rank > 0 else None,
+                              blobs[self.rank + 1] if self.rank < self.world - 1 else None)
+            self.cur, self.nxt = self.slab.tensor(0), self.slab.tensor(1)
+        else:
+            self.cur = torch.zeros((self.nzl + 2 * R) * plane, dtype=torch.float32, device=self.device)
+            self.nxt = torch.zeros_like(self.cur)
         self.comm_stream = torch.cuda.Stream(device=self.device) if self.on_cuda and self.world > 1 else None
         self.steps_done = 0
 
@@ -123,6 +141,8 @@ class ShardedStencil:
         first, last = R, R + self.nzl  # owned planes are [first, last) of the local array
         if self.world == 1:
             self.step_fn(nxt, cur, nx, ny, nzt, first, last, self.coeff)
+        elif self.slab is not None:
+            self.slab.step(self.coeff)
         else:
             lo_end = min(first + R, last)
             hi_begin = max(last - R, lo_end)

@@ -73,6 +73,14 @@ int cudadma_strided_transpose(float *dst, const float *src, int rows, int cols, 
 int cudadma_gather_scatter(void *out, const void *table, const int32_t *gather_idx, const int32_t *scatter_idx,
                            size_t n, int record_bytes, int impl, void *stream);
 
+/* The same workload with the gather done by TMA row gathers (cp.async.bulk.tensor ... tile::gather4
+ * through CudaDMAIndirect::execute_dma_gather4): four table records per instruction. The tensor map
+ * needs the table's extent, hence table_records. Same result; on B200 it measured slower than the
+ * 16-byte cp.async gather of cudadma_gather_scatter (1.63 against 1.76 TB/s on the benchmark
+ * configuration), so the latter stays the default path. gather_idx entries must be < table_records. */
+int cudadma_gather_scatter_tma(void *out, const void *table, size_t table_records, const int32_t *gather_idx,
+                               const int32_t *scatter_idx, size_t n, int record_bytes, void *stream);
+
 /* One step of the radius-4 25-point stencil on an nx x ny x nz fp32 grid (x
  * fastest), output planes [z_begin, z_end) only; reads outside the grid give
  * zero. 32 x 16 tiles with their halo come in through CudaDMAHalo, z-marching.
@@ -95,6 +103,28 @@ int cudadma_stencil25_run(float *a, float *b, int nx, int ny, int nz, const floa
  * the library workspace, run this kernel there and copy the result back. */
 int cudadma_stencil25_step_padded(float *out, const float *in, int nx, int ny, int nz, int z_begin, int z_end,
                                   const float coeff[5], int z_chunk, int impl, void *stream);
+
+/* z-sharded stencil, one process per GPU, halo planes pushed straight into the z-neighbours'
+ * memory. (The reference has no multi-GPU code; every program of it uses device 0,
+ * src/examples/stencil/cudaDMA_stencil2D.cu:62.) A slab is this rank's nzl planes of an
+ * nx x ny x nz grid plus four ghost planes on either side, in two ping-pong arrays that the
+ * library allocates so that they can be shared between processes (CUDA IPC).
+ *   create  -> export (cudadma_slab_handle_bytes() bytes to hand to both neighbours, by any
+ *   means) -> connect (with the neighbours' bytes) -> fill buffer 0 (current field; ghost planes
+ *   included) -> step, step, ... -> read buffer 0 -> destroy.
+ * One step: wait until both neighbours have finished the previous step (a flag word they write
+ * into this GPU's memory; the wait is bounded), compute the first and last four owned planes
+ * with every result stored twice, here and in the neighbour's ghost planes over NVLink, compute
+ * the interior, then publish this rank's step count to both neighbours. No collective library is
+ * involved. has_lower / has_upper say whether a neighbour exists on that side; nzl >= 8 then.
+ * cudadma_slab_buffer: which = 0 the current field, 1 the other array; (nzl + 8) * ny * nx floats. */
+int cudadma_slab_create(void **slab, int nx, int ny, int nzl, int has_lower, int has_upper);
+size_t cudadma_slab_handle_bytes(void);
+int cudadma_slab_export(void *slab, void *handles);
+int cudadma_slab_connect(void *slab, const void *lower_handles, const void *upper_handles);
+int cudadma_slab_buffer(void *slab, int which, float **ptr);
+int cudadma_slab_step(void *slab, const float coeff[5], void *stream);
+int cudadma_slab_destroy(void *slab);
 
 /* One stencil step for callers that must not allocate device memory. (No counterpart in the
  * reference, which has no host library at all.)

@@ -20,7 +20,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, nx, ny, nz, steps, q):
+def _worker(rank, world, port, nx, ny, nz, steps, exchange, q):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
@@ -30,17 +30,20 @@ def _worker(rank, world, port, nx, ny, nz, steps, q):
         from cudadma_b200.sharded import ShardedStencil
         from oracle import oracle
         field = oracle.fill_uniform(nx * ny * nz, 0xC4, 0.0, 1.0).reshape(nz, ny, nx)
-        st = ShardedStencil(nx, ny, nz)
+        st = ShardedStencil(nx, ny, nz, exchange=exchange)
         st.load(torch.from_numpy(field[st.z_lo:st.z_hi].copy()).cuda())
         got = st.run(steps).cpu().numpy().copy()
         torch.cuda.synchronize()
+        import cudadma_b200 as cd
+        assert cd.device_status() == 0, "a bounded wait gave up on rank %d" % rank
+        dist.barrier()  # nobody unmaps a neighbour's memory while the other side still steps
         q.put((rank, st.z_lo, st.z_hi, got))
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("nz,steps", [(40, 3), (19, 2)])
-def test_two_gpus_equal_one_gpu(nz, steps):
+@pytest.mark.parametrize("nz,steps,exchange", [(40, 3, "nccl"), (19, 2, "nccl"), (40, 5, "p2p"), (17, 2, "p2p")])
+def test_two_gpus_equal_one_gpu(nz, steps, exchange):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two CUDA devices")
     import cudadma_b200 as cd
@@ -49,7 +52,7 @@ def test_two_gpus_equal_one_gpu(nz, steps):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, nx, ny, nz, steps, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, nx, ny, nz, steps, exchange, q)) for r in range(world)]
     for p in procs:
         p.start()
     parts = [q.get(timeout=300) for _ in range(world)]

@@ -112,6 +112,21 @@ def test_gather_scatter_small(impl, n, table_records):
     assert not out[n * 8:].any()
 
 
+@pytest.mark.parametrize("n,table_records", [(128, 1000), (128 * 333, 1 << 16), (1 << 16, 1 << 20)])
+def test_gather_scatter_tma_gather4(n, table_records):
+    """The TMA row-gather form gives the same bytes."""
+    table = oracle.fill_uniform(table_records * 8, 0xC3, -1.0, 1.0)
+    gidx = oracle.fill_index(n, 0xC3A, table_records)
+    sidx = oracle.permutation(n, 0xC3B)
+    d_out = torch.zeros(n * 8 + 64, dtype=torch.float32, device="cuda")
+    cd.gather_scatter_tma(d_out, dev(table), table_records, dev(gidx), dev(sidx), n)
+    status_clean()
+    out = d_out.cpu().numpy()
+    exp = oracle.gather_scatter(np.zeros(n * 8, dtype=np.float32), table, gidx, sidx, 32)
+    assert np.array_equal(out[:n * 8].view(np.uint32), exp.view(np.uint32))
+    assert not out[n * 8:].any()
+
+
 @pytest.mark.parametrize("impl", IMPLS)
 def test_gather_scatter_full_size(impl):
     """2^24-record table, 2^22 indices: every output slot holds the record its index names
