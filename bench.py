@@ -522,7 +522,8 @@ def main():
     torch.cuda.empty_cache()
     if impl == "ours":
         # launches of this library per timed step: one kernel at N = 1, three (two boundary runs + interior) at N > 1
-        line["gpu_launches"] = args.steps * (1 if world == 1 else (5 if EXCHANGE == "p2p" else 3))
+        # p2p: wait kernel, stencil kernel, signal kernel; nccl: two boundary launches and the interior launch
+        line["gpu_launches"] = args.steps * (1 if world == 1 else 3)
         line["launches_total_this_process"] = cd.launch_count() - before
     else:
         line["impl"] = "reference"

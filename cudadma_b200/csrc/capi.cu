@@ -154,9 +154,9 @@ int finish_status(cudaStream_t s) {
   return w ? CUDADMA_ERR_TIMEOUT : CUDADMA_OK;
 }
 
-/* Launch of the tensor-map stencil kernel on output planes [z_begin, z_end); peer_out (may be
- * null) is a second destination for every output, at the same plane numbers. */
-int launch_stencil_native(float *out, float *peer_out, const float *in, int nx, int ny, int nz, int z_begin, int z_end,
+/* Launch of the tensor-map stencil kernel on output planes [z_begin, z_end); `peer` names second
+ * destinations for the lowest and highest planes (see stencil25::Peers). */
+int launch_stencil_native(float *out, const stencil25::Peers &peer, const float *in, int nx, int ny, int nz, int z_begin, int z_end,
                           const float coeff[5], int z_chunk, cudaStream_t s) {
   const int sms = sm_count();
   if (sms <= 0) { t_last_cuda_error = (int)cudaErrorNoDevice; return CUDADMA_ERR_CUDA; }
@@ -185,7 +185,7 @@ int launch_stencil_native(float *out, float *peer_out, const float *in, int nx, 
   if (int r = make_map_f32(&map, in, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, STENCIL25_L2PROMO)) return r;
   dim3 grid(tiles_x, tiles_y, zc);
   stencil25::tensor_kernel<<<grid, stencil25::COMPUTE_THREADS + stencil25::DMA_THREADS, stencil25::SMEM_BYTES, s>>>(
-      map, out, peer_out, nx, ny, z_begin, z_end, z_chunk, k);
+      map, out, peer, nx, ny, z_begin, z_end, z_chunk, k);
   return launched();
 }
 
@@ -409,7 +409,7 @@ int cudadma_stencil25_step(float *out, const float *in, int nx, int ny, int nz, 
   if (impl == CUDADMA_IMPL_PORTABLE)
     return portable_stencil(const_cast<float *>(in), out, nx, ny, nz, z_begin, z_end, coeff, 1, z_chunk, s);
   if (impl != CUDADMA_IMPL_NATIVE) return CUDADMA_ERR_UNSUPPORTED;
-  return launch_stencil_native(out, nullptr, in, nx, ny, nz, z_begin, z_end, coeff, z_chunk, s);
+  return launch_stencil_native(out, stencil25::Peers{nullptr, 0, nullptr, 0}, in, nx, ny, nz, z_begin, z_end, coeff, z_chunk, s);
 }
 
 int cudadma_stencil25_run(float *a, float *b, int nx, int ny, int nz, const float coeff[5], int steps, int impl,
@@ -581,7 +581,6 @@ int cudadma_slab_step(void *slab, const float coeff[5], void *stream) {
   const long long pz = (long long)nx * ny;
   float *cur = sl->buf[sl->cur], *nxt = sl->buf[sl->cur ^ 1];
   const int first = 4, last = 4 + nzl;
-  int lo_end = first, hi_begin = last;
   if (sl->has_lo || sl->has_hi) {
     /* neighbours must have finished the previous step: their copies of it are in this rank's ghost
      * planes, and they no longer read the ghost planes this step is about to overwrite */
@@ -589,20 +588,13 @@ int cudadma_slab_step(void *slab, const float coeff[5], void *stream) {
                                      sl->step);
     if (int r = launched()) return r;
   }
-  if (sl->has_lo) {
-    lo_end = first + 4;
-    /* plane z of this rank is plane z + nzl_lo of the lower neighbour (its upper ghost planes) */
-    float *peer = sl->lo_buf[sl->cur ^ 1] + (long long)sl->nzl_lo * pz;
-    if (int r = launch_stencil_native(nxt, peer, cur, nx, ny, nzt, first, lo_end, coeff, 0, s)) return r;
-  }
-  if (sl->has_hi) {
-    hi_begin = last - 4;
-    /* plane z of this rank is plane z - nzl of the upper neighbour (its lower ghost planes) */
-    float *peer = sl->hi_buf[sl->cur ^ 1] - (long long)nzl * pz;
-    if (int r = launch_stencil_native(nxt, peer, cur, nx, ny, nzt, hi_begin, last, coeff, 0, s)) return r;
-  }
-  if (lo_end < hi_begin)
-    if (int r = launch_stencil_native(nxt, nullptr, cur, nx, ny, nzt, lo_end, hi_begin, coeff, 0, s)) return r;
+  /* one launch for all owned planes; the first and last four are stored twice, here and in the
+   * neighbour's ghost planes: plane z of this rank is plane z + nzl_lo of the lower neighbour
+   * (its upper ghost planes) and plane z - nzl of the upper neighbour (its lower ghost planes) */
+  stencil25::Peers peer = {nullptr, 0, nullptr, 0};
+  if (sl->has_lo) { peer.lo = sl->lo_buf[sl->cur ^ 1] + (long long)sl->nzl_lo * pz; peer.lo_end = first + 4; }
+  if (sl->has_hi) { peer.hi = sl->hi_buf[sl->cur ^ 1] - (long long)nzl * pz; peer.hi_begin = last - 4; }
+  if (int r = launch_stencil_native(nxt, peer, cur, nx, ny, nzt, first, last, coeff, 0, s)) return r;
   if (sl->has_lo || sl->has_hi) {
     slab_signal_kernel<<<1, 1, 0, s>>>(sl->has_lo ? sl->lo_flags + 1 : nullptr, sl->has_hi ? sl->hi_flags + 0 : nullptr,
                                        sl->step + 1);

@@ -134,9 +134,14 @@ __device__ __forceinline__ void fold_plane(const float *__restrict__ win, float2
  * Output planes [z_begin, z_end) are produced, blockIdx.z taking z_chunk of them;
  * input planes outside [0, nz) read as zero. Planes are numbered kp = 0 .. depth + 7
  * from (first output plane - 4); output plane kp - 8 is stored at step kp.
- * peer_out, when not null, receives a second copy of every output at the same plane
- * index: the sharded driver points it into a z-neighbour GPU's ghost planes (plain stores
- * over NVLink), shifted so that this rank's plane numbers land on the neighbour's. */
+ * Peers: output planes below peer.lo_end are stored a second time through peer.lo, planes from
+ * peer.hi_begin on through peer.hi, at the same plane index (null pointers switch this off).
+ * The sharded driver points them into the z-neighbour GPUs' ghost planes (plain stores over
+ * NVLink), shifted so that this rank's plane numbers land on the neighbour's. */
+struct Peers {
+  float *lo; int lo_end;
+  float *hi; int hi_begin;
+};
 #if defined(STENCIL25_MAXNREG)
 __global__ void __maxnreg__(STENCIL25_MAXNREG)
 #elif defined(STENCIL25_MIN_BLOCKS)
@@ -144,7 +149,7 @@ __global__ void __launch_bounds__(COMPUTE_THREADS + DMA_THREADS, STENCIL25_MIN_B
 #else
 __global__ void __launch_bounds__(COMPUTE_THREADS + DMA_THREADS)
 #endif
-tensor_kernel(const __grid_constant__ CUtensorMap in_map, float *__restrict__ out, float *__restrict__ peer_out,
+tensor_kernel(const __grid_constant__ CUtensorMap in_map, float *__restrict__ out, const Peers peer,
               const int nx, const int ny, const int z_begin, const int z_end, const int z_chunk, const Coeffs k) {
   extern __shared__ __align__(128) unsigned char smem[];
   typedef CudaDMAHalo<float, R, true, 16> Halo;
@@ -166,7 +171,7 @@ tensor_kernel(const __grid_constant__ CUtensorMap in_map, float *__restrict__ ou
     const long long py = nx, pz = (long long)nx * ny;
     const long long cell0 = (long long)z0 * pz + (long long)(y0 + 2 * ty) * py + x0 + 4 * tx;
     float *o = out + cell0;
-    float *po = peer_out ? peer_out + cell0 : nullptr;
+
     const bool row0_ok = (x0 + 4 * tx < nx) && (y0 + 2 * ty < ny);
     const bool row1_ok = (x0 + 4 * tx < nx) && (y0 + 2 * ty + 1 < ny);
     const int win_off = (2 * ty + R) * WIN_X + 4 * tx + R;
@@ -194,9 +199,12 @@ tensor_kernel(const __grid_constant__ CUtensorMap in_map, float *__restrict__ ou
                 const float4 v1 = make_float4(r[1][0].x, r[1][0].y, r[1][1].x, r[1][1].y);
                 if (row0_ok) *reinterpret_cast<float4 *>(o + plane) = v0;
                 if (row1_ok) *reinterpret_cast<float4 *>(o + plane + py) = v1;
+                const int z = z0 + kp - 2 * R;
+                float *po = (peer.lo && z < peer.lo_end) ? peer.lo : ((peer.hi && z >= peer.hi_begin) ? peer.hi : nullptr);
                 if (po) {
-                  if (row0_ok) *reinterpret_cast<float4 *>(po + plane) = v0;
-                  if (row1_ok) *reinterpret_cast<float4 *>(po + plane + py) = v1;
+                  po += cell0 + plane;
+                  if (row0_ok) *reinterpret_cast<float4 *>(po) = v0;
+                  if (row1_ok) *reinterpret_cast<float4 *>(po + py) = v1;
                 }
               }
             }

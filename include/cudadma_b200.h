@@ -113,9 +113,9 @@ int cudadma_stencil25_step_padded(float *out, const float *in, int nx, int ny, i
  *   means) -> connect (with the neighbours' bytes) -> fill buffer 0 (current field; ghost planes
  *   included) -> step, step, ... -> read buffer 0 -> destroy.
  * One step: wait until both neighbours have finished the previous step (a flag word they write
- * into this GPU's memory; the wait is bounded), compute the first and last four owned planes
- * with every result stored twice, here and in the neighbour's ghost planes over NVLink, compute
- * the interior, then publish this rank's step count to both neighbours. No collective library is
+ * into this GPU's memory; the wait is bounded), compute all owned planes in one launch, the
+ * first and last four of them stored twice, here and in the neighbour's ghost planes over
+ * NVLink, then publish this rank's step count to both neighbours. No collective library is
  * involved. has_lower / has_upper say whether a neighbour exists on that side; nzl >= 8 then.
  * cudadma_slab_buffer: which = 0 the current field, 1 the other array; (nzl + 8) * ny * nx floats. */
 int cudadma_slab_create(void **slab, int nx, int ny, int nzl, int has_lower, int has_upper);

@@ -1,0 +1,64 @@
+"""The reference's own five stencil example kernels (src/examples/stencil/*.h of the CudaDMA
+project: warp-specialised single / double / manual buffering, non-specialised single / double),
+compiled UNCHANGED from the reference checkout twice -- against the reference header and against
+this repository's header (oracle/ref_examples.cu, oracle/Makefile) -- and run on the same seeded
+input. The two device results must agree bit for bit, and both must be the in-plane average of
+src/examples/stencil/stencil_math.h:48-86. Skipped where the libraries were not built (no
+reference checkout at build time)."""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+
+from oracle import oracle
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+OURS = os.path.join(ROOT, "oracle", "_ref", "libexamples_ours.so")
+REF = os.path.join(ROOT, "oracle", "_ref", "libexamples_ref.so")
+pytestmark = [pytest.mark.gpu,
+              pytest.mark.skipif(not (os.path.exists(OURS) and os.path.exists(REF)), reason="example libraries not built")]
+NAMES = ["warp_specialized_single_buffer", "warp_specialized_double_buffer", "warp_specialized_manual_buffer",
+         "non_warp_specialized_single_buffer", "non_warp_specialized_double_buffer"]
+R = 4
+
+
+def run(path, prefix, kid, src, dims):
+    lib = ctypes.CDLL(path)
+    fn = getattr(lib, prefix + "run")
+    fn.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                   ctypes.POINTER(ctypes.c_float)]
+    dst = np.zeros_like(src)
+    ms = ctypes.c_float(0)
+    err = fn(kid, src.ctypes.data, dst.ctypes.data, dims[0], dims[1], dims[2], ctypes.byref(ms))
+    assert err == 0, "cudaError %d" % err
+    return dst, ms.value
+
+
+def expected(src, dims):
+    """accum = centre + sum over dx, dy in 1..RADIUS-1 of the four arms, divided by 4*RADIUS + 1."""
+    x, y, z = dims
+    a = src.astype(np.float32)
+    c = a[R:R + z, R:R + y, R:R + x].copy()
+    acc = c.copy()
+    for sign, axis in ((-1, 2), (1, 2), (-1, 1), (1, 1)):  # the order stencil_math.h adds them in
+        for d in range(1, R):
+            sl = [slice(R, R + z), slice(R, R + y), slice(R, R + x), slice(None)]
+            sl[axis] = slice(R + sign * d, R + sign * d + (x if axis == 2 else y))
+            acc = acc + a[tuple(sl)]
+    return acc / np.float32(4 * R + 1)
+
+
+@pytest.mark.parametrize("kid", range(5))
+def test_reference_example_kernel_runs_unchanged_on_this_header(kid):
+    dims = (96, 16, 12)
+    shape = (dims[2] + 2 * R, dims[1] + 2 * R, dims[0] + 2 * R, 2)
+    src = oracle.fill_uniform(int(np.prod(shape)), 0xE0 + kid, -1.0, 1.0).reshape(shape)
+    ours, _ = run(OURS, "examples_ours_", kid, src, dims)
+    ref, _ = run(REF, "examples_ref_", kid, src, dims)
+    assert np.array_equal(ours.view(np.uint32), ref.view(np.uint32)), NAMES[kid]
+    inner = ours[R:R + dims[2], R:R + dims[1], R:R + dims[0]]
+    assert np.allclose(inner, expected(src, dims), rtol=1e-6, atol=1e-6)
+    border = ours.copy()
+    border[R:R + dims[2], R:R + dims[1], R:R + dims[0]] = 0
+    assert not border.any(), "wrote outside the grid"
