@@ -1023,5 +1023,20 @@ class CudaDMACustom : public CudaDMA {
 };
 typedef CudaDMACustom cudaDMACustom;
 
+/* ------------------------------------------------------------------------- */
+/* v1 spellings (include/cudaDMA.h:644, :1977, :2891): the same classes        */
+/* without the BYTES_PER_THREAD parameter, which bounded a register staging     */
+/* buffer that does not exist here. Constructor argument orders of the v1       */
+/* forms are those of the v2 forms above (cudaDMA.h:651-653, :916-920,          */
+/* :1037-1040, :1985-1996), so kernels written for v1 (the saxpy and sgemv      */
+/* examples of the reference) name these and construct them as before.          */
+/* ------------------------------------------------------------------------- */
+template <bool DO_SYNC, int ALIGNMENT, int BYTES_PER_ELMT = 0, int DMA_THREADS = 0>
+using cudaDMASequential = CudaDMASequential<DO_SYNC, ALIGNMENT, 4 * ALIGNMENT, BYTES_PER_ELMT, DMA_THREADS>;
+template <bool DO_SYNC, int ALIGNMENT, int BYTES_PER_ELMT = 0, int DMA_THREADS = 0, int NUM_ELMTS = 0>
+using cudaDMAStrided = CudaDMAStrided<DO_SYNC, ALIGNMENT, 4 * ALIGNMENT, BYTES_PER_ELMT, DMA_THREADS, NUM_ELMTS>;
+template <bool GATHER, bool DO_SYNC, int ALIGNMENT, int BYTES_PER_ELMT = 0, int DMA_THREADS = 0, int NUM_ELMTS = 0>
+using cudaDMAIndirect = CudaDMAIndirect<GATHER, DO_SYNC, ALIGNMENT, 4 * ALIGNMENT, BYTES_PER_ELMT, DMA_THREADS, NUM_ELMTS>;
+
 #undef CUDADMA_B200_XFER_OVERLOADS
 #endif /* CUDADMA_B200_CUDADMA_H */

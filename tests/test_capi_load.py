@@ -62,5 +62,24 @@ def test_header_library_is_self_contained():
         open(src, "w").write('#include "cudaDMAv2.h"\n__global__ void k(float* a){ extern __shared__ float b[];'
                              ' CudaDMASequential<true,16,64,1024,32> d(1,32,32);'
                              ' if (d.owns_this_thread()) d.execute_dma(a,b); else { d.start_async_dma(); d.wait_for_dma_finish(); a[threadIdx.x]=b[threadIdx.x]; } }\n')
+        # the v1 spellings, used the way the reference's saxpy example uses them
+        # (src/examples/saxpy/saxpy_cudaDMA_kernel.cu:276-279, src/examples/saxpy_strided/saxpy_cudaDMA_kernel.cu:54-57)
+        src1 = os.path.join(d, "v1.cu")
+        open(src1, "w").write('#include "cudaDMA.h"\n__global__ void k(float* x, float* y, const int* idx){ extern __shared__ float b[];'
+                              ' cudaDMASequential<true,16,4096,64> d0(1,128,128);'
+                              ' cudaDMAStrided<true,16,256,64,16> d1(2,128,128+64,1024);'
+                              ' cudaDMAIndirect<true,true,16,32,64,32> d2(3,128,128+128);'
+                              ' cudaDMAHalo<float,4,false,16> d3(4,32,128,128+192,32,16,512);'
+                              ' cudaDMACustom d4(5,32,128,128+224);'
+                              ' if (d0.owns_this_thread()) d0.execute_dma(x,b);'
+                              ' else if (d1.owns_this_thread()) d1.execute_dma(y,b+1024);'
+                              ' else if (d2.owns_this_thread()) d2.execute_dma(idx,x,b+2048);'
+                              ' else if (d3.owns_this_thread()) d3.execute_dma(x+4*512+4,b+4096+4*40+4);'
+                              ' else if (d4.owns_this_thread()) { d4.wait_for_dma_start(); d4.finish_async_dma(); }'
+                              ' else { d0.start_async_dma(); d1.start_async_dma(); d2.start_async_dma(); d3.start_async_dma(); d4.start_async_dma();'
+                              ' d0.wait_for_dma_finish(); d1.wait_for_dma_finish(); d2.wait_for_dma_finish(); d3.wait_for_dma_finish();'
+                              ' d4.wait_for_dma_finish(); y[threadIdx.x]=b[threadIdx.x]; } }\n')
+        subprocess.check_call([nvcc, "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-c", "-o",
+                               os.path.join(d, "v1.o"), "-I" + os.path.join(ROOT, "include", "cudadma"), src1])
         subprocess.check_call([nvcc, "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-c", "-o",
                                os.path.join(d, "t.o"), "-I" + os.path.join(ROOT, "include", "cudadma"), src])
