@@ -6,7 +6,7 @@
  * One CTA owns a 32 x 16 xy tile and a run of z planes. Its DMA warp streams
  * the tile plus its radius-4 halo (40 x 24 floats, one TMA box per plane, zero
  * fill outside the grid) into a ring of shared-memory buffers. The compute
- * threads each own a 4 (x) by PY (y) patch of the tile (PY = 2: 64 threads). Every plane is read from
+ * threads (64) each own a 4 (x) by 2 (y) patch of the tile. Every plane is read from
  * shared memory exactly once, when it arrives, and is pushed forward into the
  * nine output planes it contributes to:
  *   - its in-plane (x and y) neighbours go to the output plane of the same z;
@@ -41,14 +41,16 @@ constexpr int SLOTS = 2 * R + 1;                              /* 9 partial outpu
 #endif
 constexpr int STAGES = STENCIL25_STAGES;
 static_assert(SLOTS % STAGES == 0, "the ring size must divide nine so that stage indices stay static");
-#ifndef STENCIL25_PATCH_Y
-#define STENCIL25_PATCH_Y 2 /* rows of a thread's patch: 1 or 2 (the patch is four points wide) */
-#endif
-constexpr int PY = STENCIL25_PATCH_Y;
+constexpr int PY = 2; /* rows of a thread's patch (the patch is four points wide) */
 constexpr int COMPUTE_THREADS = (TILE_X / 4) * (TILE_Y / PY), DMA_THREADS = 32;
 constexpr int SMEM_BYTES = STAGES * PLANE_BYTES;
 
 struct Coeffs { float c[5]; };
+/* second destinations of the lowest and highest output planes (see tensor_kernel) */
+struct Peers {
+  float *lo; int lo_end;
+  float *hi; int hi_begin;
+};
 
 /* Arithmetic is done two points at a time with the packed fp32 FMA of sm_100
  * (fma.rn.f32x2 through __ffma2_rn): one issue slot for two fused multiply-adds,
@@ -73,14 +75,14 @@ __device__ __forceinline__ void static_for(F &&f, std::integer_sequence<int, I..
  * window column 4*tx + R). in_plane: the plane is itself an output plane of this
  * CTA, so its x/y neighbours are needed. c2[r] = (c_r, c_r). */
 template <int KK>
-__device__ __forceinline__ void fold_plane(const float *__restrict__ win, float2 (&acc)[SLOTS][PY][2],
+__device__ __forceinline__ void fold_plane(const float *__restrict__ win, float2 (&acc)[SLOTS][2][2],
                                            const float2 (&c2)[R + 1], const bool in_plane) {
-  Row u[PY];
-#pragma unroll
-  for (int j = 0; j < PY; ++j) u[j] = ld_row(win + j * WIN_X);
+  Row u[2];
+  u[0] = ld_row(win);
+  u[1] = ld_row(win + WIN_X);
   /* z direction: output plane KK + d gets c_|d| * u; the output plane four ahead starts here */
 #pragma unroll
-  for (int j = 0; j < PY; ++j)
+  for (int j = 0; j < 2; ++j)
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       acc[(KK + R) % SLOTS][j][h] = make_float2(c2[R].x * u[j].p[h].x, c2[R].y * u[j].p[h].y);
@@ -92,10 +94,10 @@ __device__ __forceinline__ void fold_plane(const float *__restrict__ win, float2
       }
     }
   if (in_plane) {
-    float2(&o)[PY][2] = acc[KK % SLOTS];
+    float2(&o)[2][2] = acc[KK % SLOTS];
     /* x direction: row cells x-4 .. x+7 as pairs starting at even (e) and odd (q) offsets */
 #pragma unroll
-    for (int j = 0; j < PY; ++j) {
+    for (int j = 0; j < 2; ++j) {
       const Row l = ld_row(win + j * WIN_X - 4), r = ld_row(win + j * WIN_X + 4);
       const float2 e[6] = {l.p[0], l.p[1], u[j].p[0], u[j].p[1], r.p[0], r.p[1]};
       float2 q[5];
@@ -110,18 +112,23 @@ __device__ __forceinline__ void fold_plane(const float *__restrict__ win, float2
           o[j][h] = __ffma2_rn(c2[rr], (kr & 1) ? q[kr >> 1] : e[kr >> 1], o[j][h]);
         }
     }
-    /* y direction: every window row from four above the patch to four below it is taken once (the
-     * patch's own rows from registers, the others streamed from shared memory) and added to each
-     * patch row it is within four rows of */
+    /* y direction: own rows feed each other, the eight rows around the patch are streamed */
 #pragma unroll
-    for (int w = -R; w < PY + R; ++w) {
-      const Row rw = (w >= 0 && w < PY) ? u[(w >= 0 && w < PY) ? w : 0] : ld_row(win + w * WIN_X);
+    for (int h = 0; h < 2; ++h) {
+      o[0][h] = __ffma2_rn(c2[1], u[1].p[h], o[0][h]);
+      o[1][h] = __ffma2_rn(c2[1], u[0].p[h], o[1][h]);
+    }
 #pragma unroll
-      for (int j = 0; j < PY; ++j) {
-        const int d = (w > j) ? (w - j) : (j - w);
-        if (d >= 1 && d <= R) {
+    for (int d = 1; d <= R; ++d) {
+      const Row up = ld_row(win - d * WIN_X);       /* row y0 - d: distance d from row 0, d + 1 from row 1 */
+      const Row dn = ld_row(win + (d + 1) * WIN_X); /* row y1 + d: distance d from row 1, d + 1 from row 0 */
 #pragma unroll
-          for (int h = 0; h < 2; ++h) o[j][h] = __ffma2_rn(c2[d], rw.p[h], o[j][h]);
+      for (int h = 0; h < 2; ++h) {
+        o[0][h] = __ffma2_rn(c2[d], up.p[h], o[0][h]);
+        o[1][h] = __ffma2_rn(c2[d], dn.p[h], o[1][h]);
+        if (d < R) {
+          o[1][h] = __ffma2_rn(c2[d + 1], up.p[h], o[1][h]);
+          o[0][h] = __ffma2_rn(c2[d + 1], dn.p[h], o[0][h]);
         }
       }
     }
@@ -129,6 +136,64 @@ __device__ __forceinline__ void fold_plane(const float *__restrict__ win, float2
 }
 
 #ifdef CUDADMA_B200_CUDADMA_H
+/* Compute side of a CTA: folds planes kp = 0 .. depth + 7 (numbered from first output plane - 4)
+ * and stores output plane kp - 8 at step kp. PUSH: planes below peer.lo_end / from peer.hi_begin on
+ * are stored a second time through peer.lo / peer.hi. */
+template <bool PUSH, typename RING>
+__device__ __forceinline__ void compute_side(RING &ring, const unsigned char *smem, float *__restrict__ out,
+                                             const Peers &peer, const int nx, const int ny, const int x0,
+                                             const int y0, const int z0, const int depth, const Coeffs &k) {
+  const int nplanes = depth + 2 * R;
+  const int tx = threadIdx.x & 7, ty = threadIdx.x >> 3;
+  const long long py = nx, pz = (long long)nx * ny;
+  const long long cell0 = (long long)z0 * pz + (long long)(y0 + PY * ty) * py + x0 + 4 * tx;
+  float *o = out + cell0;
+  const bool row0_ok = (x0 + 4 * tx < nx) && (y0 + PY * ty < ny);
+  const bool row1_ok = (x0 + 4 * tx < nx) && (y0 + PY * ty + 1 < ny);
+  float *const po_lo = (PUSH && peer.lo) ? peer.lo + cell0 : nullptr;
+  float *const po_hi = (PUSH && peer.hi) ? peer.hi + cell0 : nullptr;
+  const int lo_end = (PUSH && peer.lo) ? peer.lo_end : -0x7fffffff;
+  const int hi_begin = (PUSH && peer.hi) ? peer.hi_begin : 0x7fffffff;
+  const int win_off = (PY * ty + R) * WIN_X + 4 * tx + R;
+  float2 acc[SLOTS][PY][2];
+  float2 c2[R + 1];
+#pragma unroll
+  for (int r = 0; r <= R; ++r) c2[r] = make_float2(k.c[r], k.c[r]);
+#pragma unroll
+  for (int s = 0; s < STAGES; ++s) ring.stage[s].start_async_dma();
+  for (int k0 = 0; k0 < nplanes; k0 += SLOTS) {
+    static_for(
+        [&](auto kk_c) {
+          constexpr int kk = decltype(kk_c)::value;
+          const int kp = k0 + kk;
+          if (kp < nplanes) {
+            ring.stage[kk % STAGES].wait_for_dma_finish();
+            const float *win = reinterpret_cast<const float *>(smem + (kk % STAGES) * PLANE_BYTES) + win_off;
+            fold_plane<kk>(win, acc, c2, kp >= R && kp < depth + R);
+            ring.stage[kk % STAGES].start_async_dma();
+            if (kp >= 2 * R) {
+              /* output plane kp - 8 of this CTA is complete: it sits in slot (kk - 4) mod 9 */
+              const float2(&r)[2][2] = acc[(kk + SLOTS - R) % SLOTS];
+              const long long plane = (long long)(kp - 2 * R) * pz;
+              const float4 v0 = make_float4(r[0][0].x, r[0][0].y, r[0][1].x, r[0][1].y);
+              const float4 v1 = make_float4(r[1][0].x, r[1][0].y, r[1][1].x, r[1][1].y);
+              if (row0_ok) *reinterpret_cast<float4 *>(o + plane) = v0;
+              if (row1_ok) *reinterpret_cast<float4 *>(o + plane + py) = v1;
+              if (PUSH) {
+                const int z = z0 + kp - 2 * R;
+                float *po = (z < lo_end) ? po_lo : ((z >= hi_begin) ? po_hi : nullptr);
+                if (po) {
+                  if (row0_ok) *reinterpret_cast<float4 *>(po + plane) = v0;
+                  if (row1_ok) *reinterpret_cast<float4 *>(po + plane + py) = v1;
+                }
+              }
+            }
+          }
+        },
+        std::make_integer_sequence<int, SLOTS>{});
+  }
+}
+
 /* in_map: 3-D tensor map over the nx x ny x nz input (x fastest), box 40 x 24 x 1.
  * Output planes [z_begin, z_end) are produced, blockIdx.z taking z_chunk of them;
  * input planes outside [0, nz) read as zero. Planes are numbered kp = 0 .. depth + 7
@@ -137,10 +202,9 @@ __device__ __forceinline__ void fold_plane(const float *__restrict__ win, float2
  * peer.hi_begin on through peer.hi, at the same plane index (null pointers switch this off).
  * The sharded driver points them into the z-neighbour GPUs' ghost planes (plain stores over
  * NVLink), shifted so that this rank's plane numbers land on the neighbour's. */
-struct Peers {
-  float *lo; int lo_end;
-  float *hi; int hi_begin;
-};
+#ifndef STENCIL25_MIN_BLOCKS
+#define STENCIL25_MIN_BLOCKS 4 /* four CTAs per SM need at most 170 registers; a fifth would spill */
+#endif
 #if defined(STENCIL25_MAXNREG)
 __global__ void __maxnreg__(STENCIL25_MAXNREG)
 #elif defined(STENCIL25_MIN_BLOCKS)
@@ -166,49 +230,10 @@ tensor_kernel(const __grid_constant__ CUtensorMap in_map, float *__restrict__ ou
       }
     }
   } else {
-    const int tx = threadIdx.x & 7, ty = threadIdx.x >> 3;
-    const long long py = nx, pz = (long long)nx * ny;
-    const long long cell0 = (long long)z0 * pz + (long long)(y0 + PY * ty) * py + x0 + 4 * tx;
-    float *o = out + cell0;
-    bool row_ok[PY];
-#pragma unroll
-    for (int j = 0; j < PY; ++j) row_ok[j] = (x0 + 4 * tx < nx) && (y0 + PY * ty + j < ny);
-    const int win_off = (PY * ty + R) * WIN_X + 4 * tx + R;
-    float2 acc[SLOTS][PY][2];
-    float2 c2[R + 1];
-#pragma unroll
-    for (int r = 0; r <= R; ++r) c2[r] = make_float2(k.c[r], k.c[r]);
-#pragma unroll
-    for (int s = 0; s < STAGES; ++s) ring.stage[s].start_async_dma();
-    for (int k0 = 0; k0 < nplanes; k0 += SLOTS) {
-      static_for(
-          [&](auto kk_c) {
-            constexpr int kk = decltype(kk_c)::value;
-            const int kp = k0 + kk;
-            if (kp < nplanes) {
-              ring.stage[kk % STAGES].wait_for_dma_finish();
-              const float *win = reinterpret_cast<const float *>(smem + (kk % STAGES) * PLANE_BYTES) + win_off;
-              fold_plane<kk>(win, acc, c2, kp >= R && kp < depth + R);
-              ring.stage[kk % STAGES].start_async_dma();
-              if (kp >= 2 * R) {
-                /* output plane kp - 8 of this CTA is complete: it sits in slot (kk - 4) mod 9 */
-                const float2(&r)[PY][2] = acc[(kk + SLOTS - R) % SLOTS];
-                const long long plane = (long long)(kp - 2 * R) * pz;
-                const int z = z0 + kp - 2 * R;
-                float *po = (peer.lo && z < peer.lo_end) ? peer.lo : ((peer.hi && z >= peer.hi_begin) ? peer.hi : nullptr);
-#pragma unroll
-                for (int j = 0; j < PY; ++j) {
-                  const float4 v = make_float4(r[j][0].x, r[j][0].y, r[j][1].x, r[j][1].y);
-                  if (row_ok[j]) {
-                    *reinterpret_cast<float4 *>(o + plane + j * py) = v;
-                    if (po) *reinterpret_cast<float4 *>(po + cell0 + plane + j * py) = v;
-                  }
-                }
-              }
-            }
-          },
-          std::make_integer_sequence<int, SLOTS>{});
-    }
+    /* only CTAs whose planes reach into a pushed range carry the second-destination code */
+    const bool pushes = (peer.lo && z0 < peer.lo_end) || (peer.hi && z0 + depth > peer.hi_begin);
+    if (pushes) compute_side<true>(ring, smem, out, peer, nx, ny, x0, y0, z0, depth, k);
+    else compute_side<false>(ring, smem, out, peer, nx, ny, x0, y0, z0, depth, k);
   }
 }
 #endif

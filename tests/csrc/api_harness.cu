@@ -469,7 +469,33 @@ int halo_dispatch(int radius, int corners, int offset, int dimx, int dimy, int p
 
 }  // namespace
 
+#ifdef HAVE_STATUS
+/* A transfer whose start signal never comes: the compute threads leave without calling
+ * start_async_dma, so the DMA threads' wait runs out, records its code and returns. */
+__global__ void starved_kernel(const float *idata, int ncompute, int ndma) {
+  extern __shared__ float buffer[];
+  CudaDMASequential<true, 16, BPT> dma(3, ndma, ncompute, ncompute, 256);
+  if (dma.owns_this_thread()) dma.execute_dma(idata, buffer);
+}
+#endif
+
 extern "C" {
+
+#ifdef HAVE_STATUS
+/* Runs starved_kernel; returns the status word it left (0 would mean the wait never gave up),
+ * negative on a CUDA error. The context stays usable. */
+long long ENTRY(starved_wait)(void) {
+  float *d = nullptr;
+  if (cudaMalloc(&d, 1024) != cudaSuccess) return -2;
+  starved_kernel<<<1, 64, 1024>>>(d, 32, 32);
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  unsigned int w = 0;
+  if (e == cudaSuccess) e = cudadma_b200::read_status(&w, 0);
+  cudaFree(d);
+  return e == cudaSuccess ? (long long)w : -2;
+}
+#endif
 
 /* which families this build contains: bit 0 sequential/strided/indirect, bit 1 halo */
 int ENTRY(families)(void) { return (HAVE_V2 ? 1 : 0) | (HAVE_HALO ? 2 : 0); }

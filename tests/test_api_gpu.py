@@ -244,3 +244,14 @@ def test_halo_benchmark_shape():
     rng = random.Random(5)
     check_halo(1, 4, 0, 16, 0, 32, 16, 512, 128, rng)
     check_halo(1, 4, 1, 16, 0, 32, 16, 512, 32, rng)
+
+
+def test_a_wait_that_cannot_be_satisfied_gives_up_with_a_status():
+    """The compute threads never send the start signal: the DMA threads' bounded wait runs out after about
+    a second, the kernel returns, the status word names dmaID 3 and the empty wait, and the device still works."""
+    import ctypes
+    lib = harness.ours().lib
+    lib.apitest_starved_wait.restype = ctypes.c_longlong
+    w = lib.apitest_starved_wait()
+    assert w == (0x80000000 | (3 << 8) | 1), hex(w)
+    check_sequential(1, 1, 0, 0, 16, 0, 4096, 64)  # the context is intact and the status word was cleared
