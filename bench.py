@@ -33,8 +33,8 @@ NX, NY, NZ = 1024, 1024, 2048          # the sharded stencil configuration
 C4 = (512, 512, 512)                   # the single-GPU stencil configuration
 BYTES_PER_POINT = 8                    # one fp32 read + one fp32 write per point and step
 # DRAM bytes per point of stencil25::tensor_kernel: dram__bytes_read + dram__bytes_write of an ncu capture
-# of the 512^3 case (1044.0 MB per launch; summary under profiles/), which grows in proportion to the points
-STENCIL_DRAM_BYTES_PER_POINT = 1044.0e6 / 512 ** 3
+# of the 512^3 case (1041.5 MB per launch; summary under profiles/), which grows in proportion to the points
+STENCIL_DRAM_BYTES_PER_POINT = 1041.5e6 / 512 ** 3
 L2_FLUSH_BYTES = 256 << 20
 EXCHANGE = "p2p"                       # halo exchange of this repository's arm at N > 1 (--exchange)
 
@@ -447,6 +447,16 @@ def profile_case(case, reps):
         out = torch.zeros(n * 8, device="cuda")
         for _ in range(reps):
             cd.gather_scatter(out, table, gi, si, n)
+    elif case == "indirect_tma":
+        n, rec = 1 << 22, 1 << 24
+        g = torch.Generator(device="cuda")
+        g.manual_seed(0xC3A)
+        table = seeded_field(rec * 8, 0xC3)
+        gi = torch.randint(0, rec, (n,), generator=g, device="cuda", dtype=torch.int32)
+        si = torch.randperm(n, generator=g, device="cuda").to(torch.int32)
+        out = torch.zeros(n * 8, device="cuda")
+        for _ in range(reps):
+            cd.gather_scatter_tma(out, table, rec, gi, si, n)
     else:
         raise SystemExit("unknown case " + case)
     torch.cuda.synchronize()
@@ -477,7 +487,7 @@ def main():
     ap.add_argument("--exchange", default="p2p", choices=("p2p", "nccl"),
                     help="halo exchange at N > 1: peer-to-peer stores from the boundary kernel, or NCCL send/recv")
     ap.add_argument("--profile-case", default=None,
-                    help="run only a small case of one kernel (stencil_512, sequential, strided, indirect) "
+                    help="run only a small case of one kernel (stencil_512, sequential, strided, indirect, indirect_tma) "
                          "--steps times, for a profiler capture")
     args = ap.parse_args()
     global EXCHANGE

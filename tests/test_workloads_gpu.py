@@ -199,6 +199,31 @@ def test_stencil_plane_ranges_compose():
     assert torch.equal(full.view(torch.int32), parts.view(torch.int32))
 
 
+def test_slab_interface_without_neighbours_is_the_plain_stencil():
+    """The slab calls of the sharded driver on a rank with no neighbour on either side: same field, bit for bit,
+    as the plain ping-pong run (the two-rank forms of it are in tests/test_sharded_gpu.py)."""
+    nx, ny, nz, steps = 96, 48, 21, 4
+    field = oracle.fill_uniform(nx * ny * nz, 0xC4, 0.0, 1.0)
+    slab = cd.Slab(nx, ny, nz, False, False)
+    try:
+        assert len(slab.export()) == cd.lib().cudadma_slab_handle_bytes()
+        cur = slab.tensor(0).view(nz + 8, ny, nx)
+        assert not cur.any()
+        cur[4:4 + nz] = dev(field).view(nz, ny, nx)
+        for _ in range(steps):
+            slab.step()
+        got = slab.tensor(0).view(nz + 8, ny, nx)
+        a = dev(field)
+        want = cd.stencil25_run(a, torch.zeros_like(a), nx, ny, nz, steps).view(nz, ny, nx)
+        status_clean()
+        assert torch.equal(got[4:4 + nz].view(torch.int32), want.view(torch.int32))
+        assert not got[:4].any() and not got[4 + nz:].any(), "ghost planes of a rank without neighbours stay zero"
+    finally:
+        slab.destroy()
+    with pytest.raises(cd.CudaDMAError):
+        cd.Slab(nx, ny, 4, True, False)  # a rank with a neighbour needs at least eight planes
+
+
 def test_stencil_full_size_linearity_and_sample():
     """512^3, 10 steps. The operator is linear: stepping 2u equals twice stepping u exactly (scaling by two is exact
     in fp32), and a slab of the one-step result is compared with the double-precision oracle."""
