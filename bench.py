@@ -512,7 +512,7 @@ def main():
             # the reference's classes were not compiled here: time the CPU restatement, rank 0 only
             if rank == 0:
                 cb = cpu_baseline_stencil()
-                print(file=json_out, flush=True, *[json.dumps({
+                cpu_line = {
                     "impl": "reference", "metric": "stencil Gpts/s (radius-4 25-point fp32, %dx%dx%d)" % (NX, NY, NZ),
                     "value": round(cb["value"], 4), "unit": "Gpts/s", "n_gpus": world, "steps": args.steps,
                     "warmup": args.warmup, "ms_per_step": round(NX * NY * NZ / cb["value"] / 1e6, 2),
@@ -520,7 +520,8 @@ def main():
                     "data": "synthetic", "config": {"workload": "CPU restatement, " + cb["sample"]},
                     "cpu_baseline": cb,
                     "e2e": {"value": round(cb["value"], 4), "unit": "Gpts/s", "h2d_bytes_per_step": 0,
-                            "d2h_bytes_per_step": 0}})])
+                            "d2h_bytes_per_step": 0}}
+                print(json.dumps(cpu_line), file=json_out, flush=True)
             if dist.is_initialized():
                 dist.destroy_process_group()
             return
