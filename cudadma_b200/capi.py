@@ -56,6 +56,8 @@ SYMBOLS = [
      [_c.c_void_p, _c.c_size_t, _c.c_void_p, _c.c_size_t, _c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_int, _c.c_int]),
     ("cudadma_stencil25_run_host", _c.c_int,
      [_c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.POINTER(_c.c_float), _c.c_int, _c.c_int]),
+    ("cudadma_stencil25_run_host_pipelined", _c.c_int,
+     [_c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.POINTER(_c.c_float), _c.c_int, _c.c_int, _c.c_int]),
     ("cudadma_release_workspace", _c.c_int, []),
 ]
 
@@ -291,9 +293,16 @@ def gather_scatter_host(h_out, out_records, h_table, table_records, h_gather_idx
                                              _ptr(h_gather_idx), _ptr(h_scatter_idx), n, record_bytes, _IMPLS[impl]))
 
 
-def stencil25_run_host(h_out, h_in, nx, ny, nz, steps, coeff=None, impl="native"):
-    _check("cudadma_stencil25_run_host",
-           lib().cudadma_stencil25_run_host(_ptr(h_out), _ptr(h_in), nx, ny, nz, _coeffs(coeff), steps, _IMPLS[impl]))
+def stencil25_run_host(h_out, h_in, nx, ny, nz, steps, coeff=None, impl="native", chunk_planes=None):
+    """`steps` steps from and to host memory. chunk_planes: piece size of the overlapped form
+    (None = the library's choice, see cudadma_stencil25_run_host_pipelined)."""
+    if chunk_planes is None:
+        _check("cudadma_stencil25_run_host",
+               lib().cudadma_stencil25_run_host(_ptr(h_out), _ptr(h_in), nx, ny, nz, _coeffs(coeff), steps, _IMPLS[impl]))
+    else:
+        _check("cudadma_stencil25_run_host_pipelined",
+               lib().cudadma_stencil25_run_host_pipelined(_ptr(h_out), _ptr(h_in), nx, ny, nz, _coeffs(coeff), steps,
+                                                          _IMPLS[impl], chunk_planes))
 
 
 def release_workspace():

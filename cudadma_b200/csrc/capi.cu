@@ -14,6 +14,7 @@
 
 #include <atomic>
 #include <mutex>
+#include <vector>
 
 /* tuning knobs (compile-time): stages in flight per CTA and CTAs per SM of each kernel */
 #ifndef SEQ_STAGES
@@ -30,6 +31,9 @@
 #endif
 #ifndef TR_CTAS_PER_SM
 #define TR_CTAS_PER_SM 2
+#endif
+#ifndef HOST_PIPE_CHUNK_BYTES
+#define HOST_PIPE_CHUNK_BYTES ((size_t)256 << 20) /* piece of the field per upload in the overlapped host run */
 #endif
 #ifndef GS_STAGES
 #define GS_STAGES 8
@@ -230,6 +234,75 @@ int portable_stencil(float *a, float *b, int nx, int ny, int nz, int z_begin, in
   return pad_copy(cur, (steps & 1) ? b : a, nx, ny, nz, z_begin, z_end, false, s);
 }
 
+/* ---- host-buffer stencil run with copies and steps overlapped ----
+ * The field goes up in pieces of `chunk` planes on one stream while a second stream steps and a
+ * third brings finished planes down. After planes [0, Z) have arrived, step 1 can produce planes
+ * below Z - 4, step 2 planes below Z - 8 and so on (each step needs four planes above its
+ * output from the step before); once the whole field is up, every step runs on to the top.
+ * Two arrays suffice: step t writes array t mod 2 only below the planes that step t - 1 still
+ * has to read from it. Every plane is computed by the same kernel with the same operands as in
+ * the plain run, so the result is bit-identical to it. */
+cudaStream_t g_ws_up = nullptr, g_ws_down = nullptr;
+cudaEvent_t g_ws_ev_up = nullptr, g_ws_ev_step = nullptr;
+
+int pipelined_stencil_host(float *h_out, const float *h_in, float *da, float *db, int nx, int ny, int nz,
+                           const float coeff[5], int steps, int chunk, cudaStream_t s) {
+  if (!g_ws_up) CK(cudaStreamCreateWithFlags(&g_ws_up, cudaStreamNonBlocking));
+  if (!g_ws_down) CK(cudaStreamCreateWithFlags(&g_ws_down, cudaStreamNonBlocking));
+  if (!g_ws_ev_up) CK(cudaEventCreateWithFlags(&g_ws_ev_up, cudaEventDisableTiming));
+  if (!g_ws_ev_step) CK(cudaEventCreateWithFlags(&g_ws_ev_step, cudaEventDisableTiming));
+  const size_t plane = (size_t)nx * ny;
+  float *buf[2] = {da, db};
+  const float *result = buf[steps & 1];
+  const stencil25::Peers none{nullptr, 0, nullptr, 0};
+  std::vector<int> done((size_t)steps + 1, 0); /* done[t]: planes [0, done[t]) hold the field after t steps */
+  int down = 0;                               /* planes [0, down) are on their way to the host */
+  while (done[0] < nz) {
+    const int z0 = done[0], z1 = (nz - z0 < chunk) ? nz : z0 + chunk;
+    CK(cudaMemcpyAsync(da + z0 * plane, h_in + z0 * plane, (size_t)(z1 - z0) * plane * 4, cudaMemcpyHostToDevice, g_ws_up));
+    CK(cudaEventRecord(g_ws_ev_up, g_ws_up));
+    CK(cudaStreamWaitEvent(s, g_ws_ev_up, 0));
+    done[0] = z1;
+    for (int t = 1; t <= steps; ++t) {
+      int reach = done[t - 1] == nz ? nz : done[t - 1] - stencil25::R;
+      if (reach <= done[t]) break; /* nothing new for this step, so nothing for the later ones */
+      if (int r = launch_stencil_native(buf[t & 1], none, buf[(t - 1) & 1], nx, ny, nz, done[t], reach, coeff, 0, s)) return r;
+      done[t] = reach;
+    }
+    if (done[steps] > down) {
+      CK(cudaEventRecord(g_ws_ev_step, s));
+      CK(cudaStreamWaitEvent(g_ws_down, g_ws_ev_step, 0));
+      CK(cudaMemcpyAsync(h_out + down * plane, result + down * plane, (size_t)(done[steps] - down) * plane * 4,
+                         cudaMemcpyDeviceToHost, g_ws_down));
+      down = done[steps];
+    }
+  }
+  CK(cudaStreamSynchronize(g_ws_down));
+  return finish_status(s);
+}
+
+}  // namespace
+
+namespace {
+/* One launch of the gather + scatter pipeline for records of RB bytes, 128 records per buffer. */
+template <int RB, int STAGES>
+int launch_gather_scatter(char *out, const char *table, const int32_t *gidx, const int32_t *sidx, long long nbuf,
+                          int ctas_per_sm, int sms, cudaStream_t s) {
+  using namespace cudadma_b200::kernels;
+  constexpr int SMEM = STAGES * 128 * RB;
+  auto k = gather_scatter_kernel<RB, 128, STAGES>;
+  if (int r = allow_smem(k, SMEM)) return r;
+  static int fit = 0; /* resident CTAs per SM of this instantiation, asked once */
+  if (fit == 0) {
+    int f = 0;
+    CK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&f, k, GS_THREADS, SMEM));
+    fit = f < 1 ? 1 : f;
+  }
+  const long long want = (long long)(fit < ctas_per_sm ? fit : ctas_per_sm) * sms;
+  const int grid = (int)(nbuf < want ? nbuf : want);
+  k<<<grid, GS_THREADS, SMEM, s>>>(out, table, gidx, sidx, nbuf);
+  return launched();
+}
 }  // namespace
 
 extern "C" {
@@ -333,37 +406,37 @@ int cudadma_strided_transpose(float *dst, const float *src, int rows, int cols, 
 
 int cudadma_gather_scatter(void *out, const void *table, const int32_t *gather_idx, const int32_t *scatter_idx,
                            size_t n, int record_bytes, int impl, void *stream) {
-  using namespace cudadma_b200::kernels;
-
-  if (!out || !table || !gather_idx || !scatter_idx || record_bytes != 32 || (n % 128) || !aligned16(out) ||
+  const bool size_ok = record_bytes == 16 || record_bytes == 32 || record_bytes == 64 || record_bytes == 128;
+  if (!out || !table || !gather_idx || !scatter_idx || !size_ok || (n % 128) || !aligned16(out) ||
       !aligned16(table) || !aligned16(gather_idx) || !aligned16(scatter_idx))
     return CUDADMA_ERR_ARG;
+  if (impl != CUDADMA_IMPL_NATIVE && impl != CUDADMA_IMPL_PORTABLE) return CUDADMA_ERR_UNSUPPORTED;
   if (n == 0) return CUDADMA_OK;
   cudaStream_t s = (cudaStream_t)stream;
   const int sms = sm_count();
   if (sms <= 0) { t_last_cuda_error = (int)cudaErrorNoDevice; return CUDADMA_ERR_CUDA; }
   const long long nbuf = (long long)(n / 128);
+  char *o = static_cast<char *>(out);
+  const char *t = static_cast<const char *>(table);
   if (impl == CUDADMA_IMPL_NATIVE) {
-    constexpr int STAGES = GS_STAGES;
-    constexpr int SMEM = STAGES * 128 * 32;
-    auto k = gather_scatter_kernel<32, 128, STAGES>;
-    if (int r = allow_smem(k, SMEM)) return r;
-    const long long want = (long long)GS_CTAS_PER_SM * sms;
-    const int grid = (int)(nbuf < want ? nbuf : want);
-    k<<<grid, GS_THREADS, SMEM, s>>>(static_cast<char *>(out), static_cast<const char *>(table), gather_idx,
-                                     scatter_idx, nbuf);
-    return launched();
-  }
-  if (impl == CUDADMA_IMPL_PORTABLE) {
-    if (int r = portable::launch_gather_scatter(static_cast<char *>(out), static_cast<const char *>(table),
-                                                gather_idx, scatter_idx, nbuf, sms, s)) {
-      t_last_cuda_error = r;
-      return CUDADMA_ERR_CUDA;
+    /* ring depth: GS_STAGES buffers while a buffer is at most 8 KiB, half of that for 16 KiB buffers */
+    switch (record_bytes) {
+      case 16: return launch_gather_scatter<16, GS_STAGES>(o, t, gather_idx, scatter_idx, nbuf, GS_CTAS_PER_SM, sms, s);
+      case 32: return launch_gather_scatter<32, GS_STAGES>(o, t, gather_idx, scatter_idx, nbuf, GS_CTAS_PER_SM, sms, s);
+      case 64: return launch_gather_scatter<64, GS_STAGES>(o, t, gather_idx, scatter_idx, nbuf, GS_CTAS_PER_SM, sms, s);
+      default: return launch_gather_scatter<128, GS_STAGES / 2>(o, t, gather_idx, scatter_idx, nbuf, GS_CTAS_PER_SM, sms, s);
     }
-    ++g_launches;
-    return CUDADMA_OK;
   }
-  return CUDADMA_ERR_UNSUPPORTED;
+  int r;
+  switch (record_bytes) {
+    case 16: r = portable::launch_gather_scatter<16>(o, t, gather_idx, scatter_idx, nbuf, sms, s); break;
+    case 32: r = portable::launch_gather_scatter<32>(o, t, gather_idx, scatter_idx, nbuf, sms, s); break;
+    case 64: r = portable::launch_gather_scatter<64>(o, t, gather_idx, scatter_idx, nbuf, sms, s); break;
+    default: r = portable::launch_gather_scatter<128>(o, t, gather_idx, scatter_idx, nbuf, sms, s); break;
+  }
+  if (r) { t_last_cuda_error = r; return CUDADMA_ERR_CUDA; }
+  ++g_launches;
+  return CUDADMA_OK;
 }
 
 int cudadma_gather_scatter_tma(void *out, const void *table, size_t table_records, const int32_t *gather_idx,
@@ -670,17 +743,40 @@ int cudadma_gather_scatter_host(void *h_out, size_t out_records, const void *h_t
 
 int cudadma_stencil25_run_host(float *h_out, const float *h_in, int nx, int ny, int nz, const float coeff[5],
                                int steps, int impl) {
-  if (!h_out || !h_in || nx <= 0 || ny <= 0 || nz <= 0) return CUDADMA_ERR_ARG;
-  const size_t bytes = (size_t)nx * ny * nz * 4;
+  return cudadma_stencil25_run_host_pipelined(h_out, h_in, nx, ny, nz, coeff, steps, impl, 0);
+}
+
+int cudadma_stencil25_run_host_pipelined(float *h_out, const float *h_in, int nx, int ny, int nz,
+                                         const float coeff[5], int steps, int impl, int chunk_planes) {
+  if (!h_out || !h_in || !coeff || nx <= 0 || ny <= 0 || nz <= 0 || steps < 0 || chunk_planes < 0) return CUDADMA_ERR_ARG;
+  if (impl != CUDADMA_IMPL_NATIVE && impl != CUDADMA_IMPL_PORTABLE) return CUDADMA_ERR_UNSUPPORTED;
+  const size_t plane_bytes = (size_t)nx * ny * 4;
+  const size_t bytes = plane_bytes * nz;
   std::lock_guard<std::recursive_mutex> lock(g_ws_mutex);
   cudaStream_t s; void *da, *db;
   if (int r = ws_stream(&s)) return r;
   if (int r = ws_get(0, bytes, &da)) return r;
   if (int r = ws_get(1, bytes, &db)) return r;
-  CK(cudaMemcpyAsync(da, h_in, bytes, cudaMemcpyHostToDevice, s));
-  if (int r = cudadma_stencil25_run((float *)da, (float *)db, nx, ny, nz, coeff, steps, impl, s)) return r;
-  CK(cudaMemcpyAsync(h_out, (steps & 1) ? db : da, bytes, cudaMemcpyDeviceToHost, s));
-  return finish_status(s);
+  bool pipeline = impl == CUDADMA_IMPL_NATIVE && steps > 0 && !(nx & 3);
+  if (pipeline && chunk_planes == 0) {
+    /* the library's choice: pieces of HOST_PIPE_CHUNK_BYTES, and only where the wave of steps
+     * (four planes behind the upload per step) is short against the grid, so that copies and
+     * steps can overlap at all */
+    size_t c = HOST_PIPE_CHUNK_BYTES / plane_bytes;
+    chunk_planes = c < 16 ? 16 : (int)c;
+    pipeline = (long long)nz >= 4ll * chunk_planes && 8ll * steps <= nz;
+  }
+  if (!pipeline) {
+    CK(cudaMemcpyAsync(da, h_in, bytes, cudaMemcpyHostToDevice, s));
+    if (int r = cudadma_stencil25_run((float *)da, (float *)db, nx, ny, nz, coeff, steps, impl, s)) return r;
+    CK(cudaMemcpyAsync(h_out, (steps & 1) ? db : da, bytes, cudaMemcpyDeviceToHost, s));
+    return finish_status(s);
+  }
+  const int r = pipelined_stencil_host(h_out, h_in, (float *)da, (float *)db, nx, ny, nz, coeff, steps, chunk_planes, s);
+  if (r < 0) { /* leave nothing of this call in flight behind an error */
+    cudaStreamSynchronize(g_ws_up); cudaStreamSynchronize(s); cudaStreamSynchronize(g_ws_down);
+  }
+  return r;
 }
 
 /* ---- the entry point that allocates nothing ---- */

@@ -219,14 +219,20 @@ inline int launch_transpose(float *dst, const float *src, int rows, int cols, in
   return (int)cudaGetLastError();
 }
 
+template <int RECORD_BYTES = 32>
 inline int launch_gather_scatter(char *out, const char *table, const int *gidx, const int *sidx, long long nbuf,
                                  int sms, cudaStream_t s) {
   using namespace cudadma_b200::kernels;
   constexpr int STAGES = 4; /* dmaIDs 0..3 gather, 4..7 scatter: all sixteen named barriers of the reference */
-  auto k = gather_scatter_kernel<32, 128, STAGES>;
-  const long long want = 6ll * sms;
+  constexpr int SMEM = STAGES * 128 * RECORD_BYTES;
+  auto k = gather_scatter_kernel<RECORD_BYTES, 128, STAGES>;
+  if (SMEM > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const long long want = (SMEM <= 32 * 1024 ? 6ll : 3ll) * sms;
   const int grid = (int)(nbuf < want ? nbuf : want);
-  k<<<grid, GS_THREADS, STAGES * 128 * 32, s>>>(out, table, gidx, sidx, nbuf);
+  k<<<grid, GS_THREADS, SMEM, s>>>(out, table, gidx, sidx, nbuf);
   return (int)cudaGetLastError();
 }
 

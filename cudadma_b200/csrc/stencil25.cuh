@@ -160,7 +160,7 @@ __device__ __forceinline__ void compute_side(RING &ring, const unsigned char *sm
 #pragma unroll
   for (int r = 0; r <= R; ++r) c2[r] = make_float2(k.c[r], k.c[r]);
 #pragma unroll
-  for (int s = 0; s < STAGES; ++s) ring.stage[s].start_async_dma();
+  for (int s = 0; s < STAGES; ++s) ring.stage[s].start_async_dma_after_reads();
   for (int k0 = 0; k0 < nplanes; k0 += SLOTS) {
     static_for(
         [&](auto kk_c) {
@@ -170,7 +170,7 @@ __device__ __forceinline__ void compute_side(RING &ring, const unsigned char *sm
             ring.stage[kk % STAGES].wait_for_dma_finish();
             const float *win = reinterpret_cast<const float *>(smem + (kk % STAGES) * PLANE_BYTES) + win_off;
             fold_plane<kk>(win, acc, c2, kp >= R && kp < depth + R);
-            ring.stage[kk % STAGES].start_async_dma();
+            ring.stage[kk % STAGES].start_async_dma_after_reads(); /* this side never writes the ring */
             if (kp >= 2 * R) {
               /* output plane kp - 8 of this CTA is complete: it sits in slot (kk - 4) mod 9 */
               const float2(&r)[2][2] = acc[(kk + SLOTS - R) % SLOTS];

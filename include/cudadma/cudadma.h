@@ -232,7 +232,9 @@ __device__ __forceinline__ uint32_t barrier_addr(int dmaID, int which) {
 }
 
 /* Slow half of a wait: keeps polling, gives up after CUDADMA_WAIT_LIMIT_CYCLES
- * or as soon as any earlier wait of the grid has given up. */
+ * or as soon as any earlier wait of the grid has given up. (Sleeping between polls, 32 to 256 ns,
+ * and a suspend-time hint on the poll were both measured on the stencil kernel, whose DMA warps
+ * wait most of the time: no gain from the first, a 1 % loss from the second.) */
 inline __device__ __noinline__ void wait_slow(uint32_t bar, uint32_t parity, unsigned int code) {
   const long long t0 = clock64();
   unsigned int polls = 0;
@@ -365,6 +367,13 @@ class CudaDMA {
   /* compute threads: the buffer may be overwritten (or, for a scatter, read) by the DMA threads */
   __device__ __forceinline__ void start_async_dma(void) const {
     cudadma_b200::ptx::fence_proxy_async();
+    cudadma_b200::ptx::mbar_arrive_warp(m_bar_empty);
+  }
+  /* Extension (not in the reference): start_async_dma() for compute threads that have only READ the
+   * buffer since it was last filled. The proxy fence above exists to make a thread's own shared-memory
+   * WRITES visible to the bulk-copy engine; reads are ordered before the next transfer by the arrival
+   * alone, so a kernel that releases a buffer every few hundred instructions can leave the fence out. */
+  __device__ __forceinline__ void start_async_dma_after_reads(void) const {
     cudadma_b200::ptx::mbar_arrive_warp(m_bar_empty);
   }
   /* compute threads: block until the transfer has landed */

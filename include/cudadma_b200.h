@@ -69,7 +69,7 @@ int cudadma_strided_transpose(float *dst, const float *src, int rows, int cols, 
  * records of record_bytes, 128 records per shared buffer: CudaDMAIndirect
  * gather (src/tests/test_indirect/cudaDMA_test_indirect_v2.cu:661-692) then
  * CudaDMAIndirect scatter (include/cudaDMAv2.h:14021-14025).
- * n % 128 == 0; record_bytes == 32; scatter_idx must not repeat. */
+ * n % 128 == 0; record_bytes 16, 32, 64 or 128 (32 is the benchmark's size); scatter_idx must not repeat. */
 int cudadma_gather_scatter(void *out, const void *table, const int32_t *gather_idx, const int32_t *scatter_idx,
                            size_t n, int record_bytes, int impl, void *stream);
 
@@ -166,6 +166,16 @@ int cudadma_gather_scatter_host(void *h_out, size_t out_records, const void *h_t
                                 int record_bytes, int impl);
 int cudadma_stencil25_run_host(float *h_out, const float *h_in, int nx, int ny, int nz, const float coeff[5],
                                int steps, int impl);
+/* cudadma_stencil25_run_host with the piece size of its overlapped form given. With impl = native
+ * the field is uploaded in pieces of chunk_planes planes; while later pieces are still on the
+ * bus, the steps run on the planes that have arrived (step t trails the upload by 4 t planes)
+ * and finished planes go back to the host, so on a grid much deeper than 4 * steps planes the
+ * call takes about as long as the upload alone. The result is bit-identical to the plain
+ * upload / run / download sequence. chunk_planes = 0: the library's choice (256 MiB pieces; the
+ * plain sequence where the grid is too shallow to overlap anything), which is what
+ * cudadma_stencil25_run_host does. impl = portable always runs the plain sequence. */
+int cudadma_stencil25_run_host_pipelined(float *h_out, const float *h_in, int nx, int ny, int nz,
+                                         const float coeff[5], int steps, int impl, int chunk_planes);
 int cudadma_release_workspace(void);
 
 #ifdef __cplusplus

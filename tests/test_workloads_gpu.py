@@ -112,6 +112,24 @@ def test_gather_scatter_small(impl, n, table_records):
     assert not out[n * 8:].any()
 
 
+@pytest.mark.parametrize("impl", IMPLS)
+@pytest.mark.parametrize("record_bytes", [16, 64, 128])
+@pytest.mark.parametrize("n,table_records", [(128, 77), (128 * 41, 1 << 14), (1 << 15, 1 << 18)])
+def test_gather_scatter_record_sizes(impl, record_bytes, n, table_records):
+    """Records of 16, 64 and 128 bytes go through the same pipeline (the benchmark's size is 32)."""
+    w = record_bytes // 4
+    table = oracle.fill_uniform(table_records * w, 0xC30 + record_bytes, -1.0, 1.0)
+    gidx = oracle.fill_index(n, 0xC3A, table_records)
+    sidx = oracle.permutation(n, 0xC3B)
+    d_out = torch.zeros(n * w + 64, dtype=torch.float32, device="cuda")
+    cd.gather_scatter(d_out, dev(table), dev(gidx), dev(sidx), n, record_bytes, impl)
+    status_clean()
+    out = d_out.cpu().numpy()
+    exp = oracle.gather_scatter(np.zeros(n * w, dtype=np.float32), table, gidx, sidx, record_bytes)
+    assert np.array_equal(out[:n * w].view(np.uint32), exp.view(np.uint32))
+    assert not out[n * w:].any()
+
+
 @pytest.mark.parametrize("n,table_records", [(128, 1000), (128 * 333, 1 << 16), (1 << 16, 1 << 20)])
 def test_gather_scatter_tma_gather4(n, table_records):
     """The TMA row-gather form gives the same bytes."""
@@ -268,3 +286,25 @@ def test_host_buffer_forms_match_device_forms():
     cd.stencil25_run_host(r, f, 64, 32, 20, 3)
     assert rel_err(r, oracle.stencil25_f64(f, cd.STENCIL_COEFFS, 3)) <= STENCIL_TOL
     cd.release_workspace()
+
+
+@pytest.mark.parametrize("nx,ny,nz,steps,chunk", [(64, 48, 120, 3, 16), (36, 20, 50, 2, 7), (32, 16, 40, 4, 1),
+                                                  (64, 32, 30, 5, 64), (128, 64, 200, 6, 24), (32, 16, 9, 1, 4)])
+def test_stencil_host_run_overlapped_is_the_plain_run(nx, ny, nz, steps, chunk):
+    """Upload, steps and download overlapped in pieces of `chunk` planes: the same bits as the plain
+    upload / run / download sequence, from pinned and from pageable host memory, and in place."""
+    f = oracle.fill_uniform(nx * ny * nz, 0xC4 + nz, 0.0, 1.0)
+    d_a, d_b = dev(f), torch.zeros(nx * ny * nz, dtype=torch.float32, device="cuda")
+    cd.stencil25_run(d_a, d_b, nx, ny, nz, steps)
+    exp = (d_b if steps & 1 else d_a).cpu().numpy()
+    got = np.full_like(f, np.nan)
+    cd.stencil25_run_host(got, f, nx, ny, nz, steps, chunk_planes=chunk)
+    assert np.array_equal(got.view(np.uint32), exp.view(np.uint32))
+    h_in = torch.from_numpy(f).pin_memory()
+    h_out = torch.full((nx * ny * nz,), float("nan")).pin_memory()
+    cd.stencil25_run_host(h_out, h_in, nx, ny, nz, steps, chunk_planes=chunk)
+    assert np.array_equal(h_out.numpy().view(np.uint32), exp.view(np.uint32))
+    cd.stencil25_run_host(h_in, h_in, nx, ny, nz, steps, chunk_planes=chunk)
+    assert np.array_equal(h_in.numpy().view(np.uint32), exp.view(np.uint32))
+    status_clean()
+    assert rel_err(exp.reshape(nz, ny, nx), oracle.stencil25_f64(f.reshape(nz, ny, nx), cd.STENCIL_COEFFS, steps)) <= STENCIL_TOL
