@@ -338,12 +338,36 @@ def run_patterns(kind, peak):
 
 
 # ------------------------------------------------------------------ the stencil job
-def make_stencil(impl, nz_global):
+def calibrate_rates(world):
+    """Every rank times the stencil kernel alone on a 1024 x 1024 x 256 field of its own GPU, under
+    sustained load, and all ranks share the rates (Gpts/s). Power-capped GPUs of one box differ by
+    several per cent, and ranks that exchange planes every step run at the pace of the slowest:
+    slabs cut in proportion to these rates let them finish a step together."""
+    import cudadma_b200 as cd
+    import torch.distributed as dist
+    nz = 256
+    a, b = seeded_field(NX * NY * nz, 0xCA), torch.empty(NX * NY * nz, device="cuda")
+    t_end = time.perf_counter() + 0.5
+    while time.perf_counter() < t_end:  # reach the power state of a long run first
+        cd.stencil25_run(a, b, NX, NY, nz, 10)
+        torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    cd.stencil25_run(a, b, NX, NY, nz, 40)
+    e1.record()
+    torch.cuda.synchronize()
+    rate = NX * NY * nz * 40 / e0.elapsed_time(e1) / 1e6
+    rates = [None] * world
+    dist.all_gather_object(rates, round(rate, 1))
+    return rates
+
+
+def make_stencil(impl, nz_global, weights=None):
     """The sharded stencil driver with this arm's step function."""
     import cudadma_b200 as cd
     from cudadma_b200.sharded import ShardedStencil
     if impl == "ours":
-        return ShardedStencil(NX, NY, nz_global, exchange=EXCHANGE)
+        return ShardedStencil(NX, NY, nz_global, exchange=EXCHANGE, weights=weights)
     from oracle import reference as ref
 
     def step(out, inp, nx, ny, nz_total, zb, ze, coeff):
@@ -354,7 +378,15 @@ def make_stencil(impl, nz_global):
 
 def run_stencil_job(impl, args, rank, world, local, peak, peak_kind):
     import cudadma_b200 as cd
-    st = make_stencil(impl, NZ)
+    rates = None
+    if impl == "ours" and world > 1 and args.balance:
+        rates = calibrate_rates(world)
+    st = make_stencil(impl, NZ, rates)
+    planes = [st.nzl]
+    if world > 1:
+        import torch.distributed as dist
+        planes = [None] * world
+        dist.all_gather_object(planes, st.nzl)
     slab_pts = NX * NY * st.nzl
     st.load(seeded_field(slab_pts, 0xC4 + rank))
     for _ in range(max(args.warmup, 3)):
@@ -377,7 +409,7 @@ def run_stencil_job(impl, args, rank, world, local, peak, peak_kind):
     if not args.no_weak:
         del st
         torch.cuda.empty_cache()
-        stw = make_stencil(impl, 256 * world)
+        stw = make_stencil(impl, 256 * world, rates)
         stw.load(seeded_field(NX * NY * stw.nzl, 0xC4 + rank))
         for _ in range(3):
             stw.step()
@@ -386,7 +418,7 @@ def run_stencil_job(impl, args, rank, world, local, peak, peak_kind):
                 "unit": "Gpts/s", "ms_per_step": round(msw / args.steps, 4)}
         del stw
         torch.cuda.empty_cache()
-        st = make_stencil(impl, NZ)
+        st = make_stencil(impl, NZ, rates)
 
     # end to end: pinned host slab -> device, K steps with halo exchange, device -> pinned host slab
     h_in = torch.empty(slab_pts, dtype=torch.float32).pin_memory()
@@ -418,7 +450,10 @@ def run_stencil_job(impl, args, rank, world, local, peak, peak_kind):
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "sharded 25-point stencil, grid %dx%dx%d, 32x16 tiles + radius-4 halo, "
                                "4-plane halo exchange per step" % (NX, NY, NZ),
-                   "planes_per_gpu": NZ // world, "exchange": ("none" if world == 1 else "torch.distributed send/recv (NCCL)" if (impl != "ours" or EXCHANGE == "nccl")
+                   "planes_per_gpu": planes if rates else NZ // world,
+                   "slab_balance": ({"rates_gpts": rates, "note": "slabs cut in proportion to each GPU's stencil rate, "
+                                     "measured alone on a 256-plane field just before"} if rates else "equal slabs"),
+                   "exchange": ("none" if world == 1 else "torch.distributed send/recv (NCCL)" if (impl != "ours" or EXCHANGE == "nccl")
                                 else "boundary kernel stores into the neighbours' ghost planes over NVLink (CUDA IPC), flag handshake"),
                    "l2": "inputs larger than L2 (%.1f GiB per array per GPU)" % (slab_pts * 4 / 2**30),
                    "synthetic_for": "uniform[0,1) field from a seeded generator"},
@@ -504,6 +539,8 @@ def main():
     ap.add_argument("--no-patterns", action="store_true", help="skip the single-GPU data-movement patterns")
     ap.add_argument("--no-weak", action="store_true", help="skip the weak-scaling companion run")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
+    ap.add_argument("--no-balance", dest="balance", action="store_false",
+                    help="equal slabs on every GPU instead of slabs in proportion to the GPUs' measured rates")
     ap.add_argument("--exchange", default="p2p", choices=("p2p", "nccl"),
                     help="halo exchange at N > 1: peer-to-peer stores from the boundary kernel, or NCCL send/recv")
     ap.add_argument("--profile-case", default=None,

@@ -23,6 +23,8 @@ cudadma_slab_step in include/cudadma_b200.h. No collective library on the step.
 Every plane is computed by the same kernel with the same arithmetic whatever
 the sharding, so an N-rank run reproduces the 1-rank field bit for bit.
 """
+import datetime
+
 import torch
 import torch.distributed as dist
 
@@ -31,11 +33,33 @@ from . import capi
 R = 4
 
 
-def slab_bounds(nz, world, rank):
-    """Planes [lo, hi) of rank `rank`: as even as possible, earlier ranks take the remainder."""
-    base, rem = divmod(nz, world)
-    lo = rank * base + min(rank, rem)
-    return lo, lo + base + (1 if rank < rem else 0)
+class ExchangeError(RuntimeError):
+    """A halo exchange did not complete: a z-neighbour is gone or too late."""
+
+
+def slab_bounds(nz, world, rank, weights=None, min_planes=1):
+    """Planes [lo, hi) of rank `rank`. Without weights: as even as possible, earlier ranks take the
+    remainder. With weights (one positive number per rank, e.g. each GPU's measured stencil rate):
+    slab sizes in proportion to them, every slab at least min_planes deep. All ranks must pass
+    the same weights; the cut is a pure function of its arguments."""
+    if weights is None:
+        base, rem = divmod(nz, world)
+        lo = rank * base + min(rank, rem)
+        return lo, lo + base + (1 if rank < rem else 0)
+    w = [float(x) for x in weights]
+    if len(w) != world or min(w) <= 0.0:
+        raise ValueError("weights: one positive number per rank")
+    if nz < world * min_planes:
+        raise ValueError("nz=%d is too shallow for %d slabs of at least %d planes" % (nz, world, min_planes))
+    total, acc, cuts = sum(w), 0.0, [0]
+    for r in range(world):
+        acc += w[r]
+        cut = nz if r == world - 1 else int(round(nz * acc / total))
+        # keep min_planes for this slab and for each of the slabs still to come
+        cut = max(cut, cuts[-1] + min_planes)
+        cut = min(cut, nz - (world - 1 - r) * min_planes)
+        cuts.append(cut)
+    return cuts[rank], cuts[rank + 1]
 
 
 def _cuda_step(out, inp, nx, ny, nz_total, z_begin, z_end, coeff):
@@ -48,18 +72,28 @@ class ShardedStencil:
     through the C ABI (there is no CPU path in the product; tests of the host logic on
     CPU ranks pass their own step function)."""
 
-    def __init__(self, nx, ny, nz, coeff=None, device=None, group=None, step_fn=None, pad_xy=0, exchange="nccl"):
+    def __init__(self, nx, ny, nz, coeff=None, device=None, group=None, step_fn=None, pad_xy=0, exchange="nccl",
+                 weights=None, exchange_timeout=None):
         """pad_xy: zero cells kept around every plane in x and y (0 for the tensor-map kernel, which
         needs no border; 4 for kernels that read a padded array). The step function sees the padded
-        planes: nx + 2 * pad_xy by ny + 2 * pad_xy."""
+        planes: nx + 2 * pad_xy by ny + 2 * pad_xy.
+        weights: relative speed of every rank (same list on all ranks); slabs are cut in proportion,
+        so that ranks which step in lockstep finish a step together even when their GPUs do not run
+        equally fast (power-capped parts differ by several per cent). None = equal slabs.
+        exchange_timeout: seconds a rank waits on the host for its neighbours' planes before step()
+        raises ExchangeError (ranks on CPU). On CUDA devices nothing waits on the host during a
+        step: a lost neighbour ends the "nccl" exchange through the process group's own timeout,
+        and the "p2p" exchange through the bounded wait of cudadma_slab_step (status
+        CUDADMA_ERR_TIMEOUT after about two seconds)."""
         self.nx, self.ny, self.nz = nx, ny, nz
         self.pad = pad_xy
         self.coeff = tuple(capi.STENCIL_COEFFS if coeff is None else coeff)
         self.group = group
+        self.exchange_timeout = exchange_timeout
         self.distributed = dist.is_available() and dist.is_initialized()
         self.rank = dist.get_rank(group) if self.distributed else 0
         self.world = dist.get_world_size(group) if self.distributed else 1
-        self.z_lo, self.z_hi = slab_bounds(nz, self.world, self.rank)
+        self.z_lo, self.z_hi = slab_bounds(nz, self.world, self.rank, weights, 2 * R if self.world > 1 else 1)
         self.nzl = self.z_hi - self.z_lo
         if self.world > 1 and self.nzl < R:
             raise ValueError("every rank needs at least %d planes (nz=%d over %d ranks)" % (R, nz, self.world))
@@ -126,12 +160,26 @@ class ShardedStencil:
             ops.append(dist.P2POp(dist.irecv, self._planes(buf, R + self.nzl, R), up, self.group))
         return ops
 
+    def _wait(self, works):
+        if self.on_cuda or self.exchange_timeout is None:
+            for w in works:
+                w.wait()  # on CUDA: the current stream waits for the exchange, the host does not block
+            return
+        limit = datetime.timedelta(seconds=float(self.exchange_timeout))
+        for w in works:
+            try:
+                done = w.wait(limit)
+            except RuntimeError as e:
+                raise ExchangeError("rank %d, step %d: %s" % (self.rank, self.steps_done + 1, e)) from e
+            if done is False:
+                raise ExchangeError("rank %d, step %d: no planes from a neighbour within %.1f s"
+                                    % (self.rank, self.steps_done + 1, float(self.exchange_timeout)))
+
     def _exchange(self, buf, wait):
         ops = self._exchange_ops(buf)
         works = dist.batch_isend_irecv(ops) if ops else []
         if wait:
-            for w in works:
-                w.wait()
+            self._wait(works)
         return works
 
     # -- time stepping -----------------------------------------------------
@@ -158,8 +206,7 @@ class ShardedStencil:
                 works = self._exchange(nxt, wait=False)
             if lo_end < hi_begin:
                 self.step_fn(nxt, cur, nx, ny, nzt, lo_end, hi_begin, self.coeff)
-            for w in works:
-                w.wait()  # on CUDA: the main stream waits for the exchange, the host does not block
+            self._wait(works)
             if self.on_cuda:
                 torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
         self.cur, self.nxt = nxt, cur

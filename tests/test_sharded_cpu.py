@@ -26,6 +26,25 @@ def test_slab_bounds_cover_the_grid():
             assert max(h - l for l, h in b) - min(h - l for l, h in b) <= 1
 
 
+def test_weighted_slab_bounds():
+    """Slabs in proportion to the ranks' speeds: they cover the grid, respect the minimum depth,
+    follow the weights, and equal weights give (nearly) the even cut."""
+    for nz, w, least in ((2048, [1.0, 0.9, 1.1, 1.0, 0.95, 1.05, 1.0, 1.0], 8), (64, [5.0, 1.0, 1.0], 8),
+                         (24, [1.0, 100.0, 1.0], 8), (33, [1.0, 1.0], 1)):
+        b = [sharded.slab_bounds(nz, len(w), r, w, least) for r in range(len(w))]
+        assert b[0][0] == 0 and b[-1][1] == nz
+        assert all(b[i][1] == b[i + 1][0] for i in range(len(w) - 1))
+        assert all(h - l >= least for l, h in b)
+    b = [sharded.slab_bounds(2048, 4, r, [1.0, 2.0, 1.0, 4.0], 8) for r in range(4)]
+    assert [h - l for l, h in b] == [256, 512, 256, 1024]
+    even = [sharded.slab_bounds(2048, 8, r) for r in range(8)]
+    assert [sharded.slab_bounds(2048, 8, r, [3.0] * 8, 8) for r in range(8)] == even
+    with pytest.raises(ValueError):
+        sharded.slab_bounds(16, 4, 0, [1.0] * 4, 8)
+    with pytest.raises(ValueError):
+        sharded.slab_bounds(64, 2, 0, [1.0, 0.0], 8)
+
+
 def test_refuses_to_run_without_cuda_or_step_function():
     if torch.cuda.is_available():
         pytest.skip("a CUDA device is present")
@@ -47,13 +66,13 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, nx, ny, nz, steps, q):
+def _worker(rank, world, port, nx, ny, nz, steps, q, weights=None):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         field = oracle.fill_uniform(nx * ny * nz, 0xC4, 0.0, 1.0).reshape(nz, ny, nx)
-        st = sharded.ShardedStencil(nx, ny, nz, COEFF, device="cpu", step_fn=oracle_step)
+        st = sharded.ShardedStencil(nx, ny, nz, COEFF, device="cpu", step_fn=oracle_step, weights=weights)
         st.load(torch.from_numpy(field[st.z_lo:st.z_hi].copy()))
         got = st.run(steps).numpy().copy()
         q.put((rank, st.z_lo, st.z_hi, got))
@@ -61,13 +80,13 @@ def _worker(rank, world, port, nx, ny, nz, steps, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,nz", [(2, 24), (3, 29), (2, 9)])
-def test_sharded_equals_single_rank_bit_for_bit(world, nz):
+@pytest.mark.parametrize("world,nz,weights", [(2, 24, None), (3, 29, None), (2, 9, None), (3, 40, (1.0, 2.0, 1.5))])
+def test_sharded_equals_single_rank_bit_for_bit(world, nz, weights):
     nx, ny, steps = 16, 12, 3
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, nx, ny, nz, steps, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, nx, ny, nz, steps, q, weights)) for r in range(world)]
     for p in procs:
         p.start()
     parts = [q.get(timeout=120) for _ in range(world)]
@@ -80,3 +99,43 @@ def test_sharded_equals_single_rank_bit_for_bit(world, nz):
         cur = oracle.stencil25_step_f32(cur, COEFF)
     for rank, lo, hi, got in parts:
         assert np.array_equal(got.view(np.uint32), cur[lo:hi].view(np.uint32)), "rank %d differs" % rank
+
+
+def _lost_neighbour_worker(rank, world, port, q, release):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    nx, ny, nz = 16, 12, 24
+    field = oracle.fill_uniform(nx * ny * nz, 0xC4, 0.0, 1.0).reshape(nz, ny, nx)
+    st = sharded.ShardedStencil(nx, ny, nz, COEFF, device="cpu", step_fn=oracle_step, exchange_timeout=2.0)
+    st.load(torch.from_numpy(field[st.z_lo:st.z_hi].copy()))
+    st.step()
+    if rank == 1:
+        # this rank stops taking part after the first step, without leaving the group
+        q.put((rank, "idle"))
+        release.wait(300)  # stays alive, and silent, until the other rank has given up on it
+        os._exit(0)
+    try:
+        st.step()
+        q.put((rank, "no error"))
+    except sharded.ExchangeError as e:
+        q.put((rank, "ExchangeError: %s" % e))
+    os._exit(0)  # the group is not usable after a lost exchange; leave without its teardown
+
+
+def test_lost_neighbour_is_reported_by_the_exchange_deadline():
+    """A rank whose z-neighbour stops stepping gets ExchangeError from step() within the deadline
+    instead of waiting for ever (the failure is made on the host: the other rank just idles)."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    release = ctx.Event()
+    procs = [ctx.Process(target=_lost_neighbour_worker, args=(r, 2, port, q, release)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = dict(q.get(timeout=240) for _ in range(2))
+    release.set()
+    for p in procs:
+        p.join(timeout=30)
+    assert got[1] == "idle"
+    assert got[0].startswith("ExchangeError: rank 0, step 2"), got[0]

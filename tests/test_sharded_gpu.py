@@ -20,7 +20,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, nx, ny, nz, steps, exchange, q):
+def _worker(rank, world, port, nx, ny, nz, steps, exchange, q, weights=None):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
@@ -30,7 +30,7 @@ def _worker(rank, world, port, nx, ny, nz, steps, exchange, q):
         from cudadma_b200.sharded import ShardedStencil
         from oracle import oracle
         field = oracle.fill_uniform(nx * ny * nz, 0xC4, 0.0, 1.0).reshape(nz, ny, nx)
-        st = ShardedStencil(nx, ny, nz, exchange=exchange)
+        st = ShardedStencil(nx, ny, nz, exchange=exchange, weights=weights)
         st.load(torch.from_numpy(field[st.z_lo:st.z_hi].copy()).cuda())
         got = st.run(steps).cpu().numpy().copy()
         torch.cuda.synchronize()
@@ -42,8 +42,10 @@ def _worker(rank, world, port, nx, ny, nz, steps, exchange, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("nz,steps,exchange", [(40, 3, "nccl"), (19, 2, "nccl"), (40, 5, "p2p"), (17, 2, "p2p")])
-def test_two_gpus_equal_one_gpu(nz, steps, exchange):
+@pytest.mark.parametrize("nz,steps,exchange,weights",
+                         [(40, 3, "nccl", None), (19, 2, "nccl", None), (40, 5, "p2p", None), (17, 2, "p2p", None),
+                          (48, 4, "p2p", (1.0, 1.7)), (48, 3, "nccl", (2.1, 1.0))])
+def test_two_gpus_equal_one_gpu(nz, steps, exchange, weights):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two CUDA devices")
     import cudadma_b200 as cd
@@ -52,7 +54,7 @@ def test_two_gpus_equal_one_gpu(nz, steps, exchange):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, nx, ny, nz, steps, exchange, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, nx, ny, nz, steps, exchange, q, weights)) for r in range(world)]
     for p in procs:
         p.start()
     parts = [q.get(timeout=300) for _ in range(world)]
