@@ -137,8 +137,8 @@ __device__ __forceinline__ void fold_plane(const float *__restrict__ win, float2
 
 #ifdef CUDADMA_B200_CUDADMA_H
 /* Compute side of a CTA: folds planes kp = 0 .. depth + 7 (numbered from first output plane - 4)
- * and stores output plane kp - 8 at step kp. PUSH: planes below peer.lo_end / from peer.hi_begin on
- * are stored a second time through peer.lo / peer.hi. */
+ * and stores output plane kp - 8 at step kp. PUSH: afterwards, planes below peer.lo_end / from
+ * peer.hi_begin on are stored a second time through peer.lo / peer.hi. */
 template <bool PUSH, typename RING>
 __device__ __forceinline__ void compute_side(RING &ring, const unsigned char *smem, float *__restrict__ out,
                                              const Peers &peer, const int nx, const int ny, const int x0,
@@ -150,10 +150,6 @@ __device__ __forceinline__ void compute_side(RING &ring, const unsigned char *sm
   float *o = out + cell0;
   const bool row0_ok = (x0 + 4 * tx < nx) && (y0 + PY * ty < ny);
   const bool row1_ok = (x0 + 4 * tx < nx) && (y0 + PY * ty + 1 < ny);
-  float *const po_lo = (PUSH && peer.lo) ? peer.lo + cell0 : nullptr;
-  float *const po_hi = (PUSH && peer.hi) ? peer.hi + cell0 : nullptr;
-  const int lo_end = (PUSH && peer.lo) ? peer.lo_end : -0x7fffffff;
-  const int hi_begin = (PUSH && peer.hi) ? peer.hi_begin : 0x7fffffff;
   const int win_off = (PY * ty + R) * WIN_X + 4 * tx + R;
   float2 acc[SLOTS][PY][2];
   float2 c2[R + 1];
@@ -179,18 +175,29 @@ __device__ __forceinline__ void compute_side(RING &ring, const unsigned char *sm
               const float4 v1 = make_float4(r[1][0].x, r[1][0].y, r[1][1].x, r[1][1].y);
               if (row0_ok) *reinterpret_cast<float4 *>(o + plane) = v0;
               if (row1_ok) *reinterpret_cast<float4 *>(o + plane + py) = v1;
-              if (PUSH) {
-                const int z = z0 + kp - 2 * R;
-                float *po = (z < lo_end) ? po_lo : ((z >= hi_begin) ? po_hi : nullptr);
-                if (po) {
-                  if (row0_ok) *reinterpret_cast<float4 *>(po + plane) = v0;
-                  if (row1_ok) *reinterpret_cast<float4 *>(po + plane + py) = v1;
-                }
-              }
             }
           }
         },
         std::make_integer_sequence<int, SLOTS>{});
+  }
+  if (PUSH) {
+    /* Second destinations. Kept out of the plane loop, which is tight on registers: every thread
+     * reads back the cells it has just stored itself (its own stores are visible to it, and
+     * still in cache) for the few planes of this CTA that lie in a pushed range, and stores
+     * them again through the peer pointer. */
+#pragma unroll 1
+    for (int side = 0; side < 2; ++side) {
+      float *const pb = side ? peer.hi : peer.lo;
+      if (!pb) continue;
+      const int zb = side ? (peer.hi_begin > z0 ? peer.hi_begin : z0) : z0;
+      const int ze = side ? z0 + depth : (peer.lo_end < z0 + depth ? peer.lo_end : z0 + depth);
+#pragma unroll 1
+      for (int z = zb; z < ze; ++z) {
+        const long long plane = (long long)(z - z0) * pz;
+        if (row0_ok) *reinterpret_cast<float4 *>(pb + cell0 + plane) = *reinterpret_cast<const float4 *>(o + plane);
+        if (row1_ok) *reinterpret_cast<float4 *>(pb + cell0 + plane + py) = *reinterpret_cast<const float4 *>(o + plane + py);
+      }
+    }
   }
 }
 
@@ -230,7 +237,8 @@ tensor_kernel(const __grid_constant__ CUtensorMap in_map, float *__restrict__ ou
       }
     }
   } else {
-    /* only CTAs whose planes reach into a pushed range carry the second-destination code */
+    /* Only CTAs whose planes reach into a pushed range run the instantiation with the second
+     * stores behind its loop (one body for all measured 1 % slower without peers). */
     const bool pushes = (peer.lo && z0 < peer.lo_end) || (peer.hi && z0 + depth > peer.hi_begin);
     if (pushes) compute_side<true>(ring, smem, out, peer, nx, ny, x0, y0, z0, depth, k);
     else compute_side<false>(ring, smem, out, peer, nx, ny, x0, y0, z0, depth, k);
