@@ -435,7 +435,7 @@ def run_stencil_job(impl, args, rank, world, local, peak, peak_kind):
     e2e = {"value": round(pts * args.steps / e2e_s / 1e9, 3), "unit": "Gpts/s",
            "h2d_bytes_per_step": slab_pts * 4 // args.steps, "d2h_bytes_per_step": slab_pts * 4 // args.steps,
            "note": ("whole job through ShardedStencil.run_host, which on one GPU is the C-ABI call "
-                    "cudadma_stencil25_run_host: pinned host field up in 256 MiB pieces, %d steps trailing the "
+                    "cudadma_stencil25_run_host: pinned host field up in 128 MiB pieces, %d steps trailing the "
                     "upload, finished planes down, all overlapped; bytes divided by the steps" % args.steps)
                    if (world == 1 and impl == "ours") else
                    ("whole job through ShardedStencil.run_host: the slab is uploaded once, stepped %d times and "

@@ -33,7 +33,7 @@
 #define TR_CTAS_PER_SM 2
 #endif
 #ifndef HOST_PIPE_CHUNK_BYTES
-#define HOST_PIPE_CHUNK_BYTES ((size_t)256 << 20) /* piece of the field per upload in the overlapped host run */
+#define HOST_PIPE_CHUNK_BYTES ((size_t)128 << 20) /* piece of the field per upload in the overlapped host run */
 #endif
 #ifndef GS_STAGES
 #define GS_STAGES 8

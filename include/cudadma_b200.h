@@ -171,7 +171,7 @@ int cudadma_stencil25_run_host(float *h_out, const float *h_in, int nx, int ny, 
  * bus, the steps run on the planes that have arrived (step t trails the upload by 4 t planes)
  * and finished planes go back to the host, so on a grid much deeper than 4 * steps planes the
  * call takes about as long as the upload alone. The result is bit-identical to the plain
- * upload / run / download sequence. chunk_planes = 0: the library's choice (256 MiB pieces; the
+ * upload / run / download sequence. chunk_planes = 0: the library's choice (128 MiB pieces; the
  * plain sequence where the grid is too shallow to overlap anything), which is what
  * cudadma_stencil25_run_host does. impl = portable always runs the plain sequence. */
 int cudadma_stencil25_run_host_pipelined(float *h_out, const float *h_in, int nx, int ny, int nz,
