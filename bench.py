@@ -33,7 +33,7 @@ NX, NY, NZ = 1024, 1024, 2048          # the sharded stencil configuration
 C4 = (512, 512, 512)                   # the single-GPU stencil configuration
 BYTES_PER_POINT = 8                    # one fp32 read + one fp32 write per point and step
 # DRAM bytes per point of stencil25::tensor_kernel: dram__bytes_read + dram__bytes_write of an ncu capture
-# of the 512^3 case (1041.5 MB per launch; summary under profiles/), which grows in proportion to the points
+# of the 512^3 case (1046.8 MB per launch; summary under profiles/), which grows in proportion to the points
 STENCIL_DRAM_BYTES_PER_POINT = 1046.8e6 / 512 ** 3
 L2_FLUSH_BYTES = 256 << 20
 EXCHANGE = "p2p"                       # halo exchange of this repository's arm at N > 1 (--exchange)
@@ -242,6 +242,19 @@ def run_patterns(kind, peak):
         f()
     ms, best = median_launch_ms(f, 30, flush)
     res["sequential_64MiB"] = entry(ms, best, 2 * n * 4)
+    # The same 64 MiB job back to back over 12 different array pairs (1.5 GiB in all, so nothing is found
+    # in L2 either): one event pair around 12 launches, which takes the event pair's own microseconds
+    # (a tenth of such a short launch) out of the figure.
+    pairs = [(seeded_field(n, 0xC10 + i), torch.empty(n, device="cuda")) for i in range(12)]
+    if kind == "reference":
+        rot = lambda: [ref.seq_copy(d, s_, n * 4) for s_, d in pairs]
+    else:
+        rot = lambda: [cd.seq_copy(d, s_, n * 4, 16384, kind) for s_, d in pairs]
+    rot()
+    msr, bestr = median_launch_ms(rot, 10)
+    res["sequential_64MiB"]["rotating_gbs"] = round(2 * n * 4 * len(pairs) / msr / 1e6, 1)
+    res["sequential_64MiB"]["rotating_frac_of_peak"] = round(2 * n * 4 * len(pairs) / msr / 1e6 / peak, 4)
+    del pairs
     # the same kernel on 1 GiB, where launch and tail effects no longer dominate
     nb = 1 << 28
     big_s, big_d = seeded_field(nb, 0xC1), torch.empty(nb, device="cuda")
@@ -441,6 +454,15 @@ def run_stencil_job(impl, args, rank, world, local, peak, peak_kind):
                    ("whole job through ShardedStencil.run_host: the slab is uploaded once, stepped %d times and "
                     "downloaded once; bytes are per rank, divided by the steps" % args.steps),
            "seconds": round(e2e_s, 4)}
+    if world == 1 and impl == "ours":
+        # the overlapped host run against the plain device run on the same input, all 2^31 points
+        st.load(h_in)
+        want = st.run(args.steps).reshape(-1)
+        same, piece = True, 1 << 28
+        for i in range(0, slab_pts, piece):
+            same = same and torch.equal(want[i:i + piece].view(torch.int32),
+                                        h_out[i:i + piece].to("cuda", non_blocking=True).view(torch.int32))
+        e2e["parity"] = "pass (bit-identical to the device-resident run)" if same else "FAIL"
     del h_in, h_out
 
     line = {
