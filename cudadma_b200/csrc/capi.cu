@@ -129,13 +129,41 @@ int allow_smem(K kernel, int bytes) {
   return CUDADMA_OK;
 }
 
-/* ---- grow-only device workspace for the host-buffer forms ---- */
+/* ---- grow-only device workspace for the host-buffer forms ----
+ * One workspace per process, on the device that was current when it was last used: a call made
+ * with another device current drops it (arrays, streams, events) and starts a new one there. */
 std::recursive_mutex g_ws_mutex;
 void *g_ws[4] = {nullptr, nullptr, nullptr, nullptr};
 size_t g_ws_bytes[4] = {0, 0, 0, 0};
+int g_ws_device = -1;
 cudaStream_t g_ws_stream = nullptr;
+cudaStream_t g_ws_up = nullptr, g_ws_down = nullptr;          /* copy streams of the overlapped host run */
+cudaEvent_t g_ws_ev_up = nullptr, g_ws_ev_step = nullptr;
 
+void ws_drop() {
+  for (int i = 0; i < 4; ++i) {
+    if (g_ws[i]) cudaFree(g_ws[i]);
+    g_ws[i] = nullptr; g_ws_bytes[i] = 0;
+  }
+  if (g_ws_stream) cudaStreamDestroy(g_ws_stream);
+  if (g_ws_up) cudaStreamDestroy(g_ws_up);
+  if (g_ws_down) cudaStreamDestroy(g_ws_down);
+  if (g_ws_ev_up) cudaEventDestroy(g_ws_ev_up);
+  if (g_ws_ev_step) cudaEventDestroy(g_ws_ev_step);
+  g_ws_stream = g_ws_up = g_ws_down = nullptr;
+  g_ws_ev_up = g_ws_ev_step = nullptr;
+}
+int ws_bind_device() {
+  int dev = -1;
+  CK(cudaGetDevice(&dev));
+  if (dev != g_ws_device) {
+    if (g_ws_device >= 0) ws_drop();
+    g_ws_device = dev;
+  }
+  return CUDADMA_OK;
+}
 int ws_get(int slot, size_t bytes, void **out) {
+  if (int r = ws_bind_device()) return r;
   if (g_ws_bytes[slot] < bytes) {
     if (g_ws[slot]) cudaFree(g_ws[slot]);
     g_ws[slot] = nullptr; g_ws_bytes[slot] = 0;
@@ -147,6 +175,7 @@ int ws_get(int slot, size_t bytes, void **out) {
   return CUDADMA_OK;
 }
 int ws_stream(cudaStream_t *s) {
+  if (int r = ws_bind_device()) return r;
   if (!g_ws_stream) CK(cudaStreamCreateWithFlags(&g_ws_stream, cudaStreamNonBlocking));
   *s = g_ws_stream;
   return CUDADMA_OK;
@@ -242,9 +271,6 @@ int portable_stencil(float *a, float *b, int nx, int ny, int nz, int z_begin, in
  * Two arrays suffice: step t writes array t mod 2 only below the planes that step t - 1 still
  * has to read from it. Every plane is computed by the same kernel with the same operands as in
  * the plain run, so the result is bit-identical to it. */
-cudaStream_t g_ws_up = nullptr, g_ws_down = nullptr;
-cudaEvent_t g_ws_ev_up = nullptr, g_ws_ev_step = nullptr;
-
 int pipelined_stencil_host(float *h_out, const float *h_in, float *da, float *db, int nx, int ny, int nz,
                            const float coeff[5], int steps, int chunk, cudaStream_t s) {
   if (!g_ws_up) CK(cudaStreamCreateWithFlags(&g_ws_up, cudaStreamNonBlocking));
@@ -840,10 +866,8 @@ int cudadma_stencil25_step_noalloc(float *out, const float *in, int nx, int ny, 
 
 int cudadma_release_workspace(void) {
   std::lock_guard<std::recursive_mutex> lock(g_ws_mutex);
-  for (int i = 0; i < 4; ++i) {
-    if (g_ws[i]) cudaFree(g_ws[i]);
-    g_ws[i] = nullptr; g_ws_bytes[i] = 0;
-  }
+  ws_drop();
+  g_ws_device = -1;
   return CUDADMA_OK;
 }
 

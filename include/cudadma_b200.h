@@ -157,8 +157,10 @@ int cudadma_stencil25_step_noalloc(float *out, const float *in, int nx, int ny, 
 /* Host-buffer forms: the same workloads for callers that hold their data in
  * host memory. Inputs are copied to the device, the kernel runs, the result
  * is copied back; the call returns when the result is in h_* memory. Device
- * staging memory is a grow-only workspace kept by the library
- * (cudadma_release_workspace() frees it). Pinned host memory copies fastest. */
+ * staging memory is a grow-only workspace kept by the library on the device
+ * that is current at the call (one per process: a call with another device
+ * current moves it there; cudadma_release_workspace() frees it). The calls
+ * serialise on a lock. Pinned host memory copies fastest. */
 int cudadma_seq_copy_host(void *h_dst, const void *h_src, size_t bytes, int chunk_bytes, int impl);
 int cudadma_strided_transpose_host(float *h_dst, const float *h_src, int rows, int cols, int impl);
 int cudadma_gather_scatter_host(void *h_out, size_t out_records, const void *h_table, size_t table_records,
