@@ -217,6 +217,40 @@ class ShardedStencil:
             self.step()
         return self.owned()
 
+    # -- checkpoint / restart ----------------------------------------------
+    _MAGIC = b"CDB200S1"
+
+    def save(self, path):
+        """Writes this rank's owned planes and the step count to `path` (one file per rank; raw
+        little-endian: magic, nx, ny, nz, z_lo, z_hi, steps_done as int64, then the float32 planes).
+        Ghost planes are not stored: restore() exchanges them again."""
+        import numpy as np
+        if self.on_cuda:
+            torch.cuda.current_stream(self.device).synchronize()
+        planes = self.owned().contiguous().cpu().numpy()
+        head = np.array([self.nx, self.ny, self.nz, self.z_lo, self.z_hi, self.steps_done], dtype="<i8")
+        with open(path, "wb") as f:
+            f.write(self._MAGIC)
+            f.write(head.tobytes())
+            f.write(planes.astype("<f4", copy=False).tobytes())
+
+    def restore(self, path):
+        """Reads a file written by save() for the same grid and the same slab, refills the ghost
+        planes from the neighbours (every rank must call it) and continues from the stored step."""
+        import numpy as np
+        with open(path, "rb") as f:
+            if f.read(len(self._MAGIC)) != self._MAGIC:
+                raise ValueError("%s is not a slab checkpoint" % path)
+            head = np.frombuffer(f.read(6 * 8), dtype="<i8")
+            if tuple(head[:5]) != (self.nx, self.ny, self.nz, self.z_lo, self.z_hi):
+                raise ValueError("%s holds planes [%d, %d) of a %d x %d x %d grid, not this rank's slab"
+                                 % (path, head[3], head[4], head[0], head[1], head[2]))
+            planes = np.frombuffer(f.read(), dtype="<f4")
+        if planes.size != self.nzl * self.ny * self.nx:
+            raise ValueError("%s is truncated" % path)
+        self.load(torch.from_numpy(planes.copy()))
+        self.steps_done = int(head[5])
+
     def run_host(self, h_out, h_in, steps):
         """The whole job from and to host memory (pinned tensors copy fastest): upload the slab,
         `steps` steps, download the slab. Returns when h_out holds the result.

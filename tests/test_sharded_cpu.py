@@ -139,3 +139,48 @@ def test_lost_neighbour_is_reported_by_the_exchange_deadline():
         p.join(timeout=30)
     assert got[1] == "idle"
     assert got[0].startswith("ExchangeError: rank 0, step 2"), got[0]
+
+
+def _checkpoint_worker(rank, world, port, tmpdir, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        nx, ny, nz = 16, 12, 26
+        field = oracle.fill_uniform(nx * ny * nz, 0xC4, 0.0, 1.0).reshape(nz, ny, nx)
+        path = os.path.join(tmpdir, "slab%d.bin" % rank)
+        a = sharded.ShardedStencil(nx, ny, nz, COEFF, device="cpu", step_fn=oracle_step)
+        a.load(torch.from_numpy(field[a.z_lo:a.z_hi].copy()))
+        a.run(2)
+        a.save(path)
+        straight = a.run(2).numpy().copy()
+        b = sharded.ShardedStencil(nx, ny, nz, COEFF, device="cpu", step_fn=oracle_step)
+        b.restore(path)
+        resumed_at = b.steps_done
+        resumed = b.run(2).numpy().copy()
+        wrong = sharded.ShardedStencil(nx, ny, nz + 2, COEFF, device="cpu", step_fn=oracle_step)
+        try:
+            wrong.restore(path)
+            refused = False
+        except ValueError:
+            refused = True
+        q.put((rank, resumed_at, b.steps_done, bool(np.array_equal(straight.view(np.uint32), resumed.view(np.uint32))), refused))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_checkpoint_restart_continues_bit_for_bit(tmp_path):
+    """save() after two steps, restore() into a new object, two more steps: the same bits as four
+    steps straight through; a checkpoint of another grid is refused."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_checkpoint_worker, args=(r, 2, port, str(tmp_path), q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=240) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, resumed_at, steps_done, same, refused in got:
+        assert resumed_at == 2 and steps_done == 4 and same and refused, (rank, resumed_at, steps_done, same, refused)
