@@ -95,11 +95,13 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_n(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
-/* One arrival operation for all lanes of the warp that are executing this call together:
- * the lanes synchronise (which orders their earlier shared-memory accesses before the
- * arrival), then the lowest of them arrives once with their number as the count. */
+/* Arrival of the calling thread. Every thread arrives for itself: one arrival per warp with the
+ * lane count (CUDADMA_WARP_AGGREGATED_ARRIVE) saves mbarrier operations but puts a warp
+ * synchronisation, a vote and a population count into the release -> refill -> consume chain, and
+ * measured slower wherever it made a difference (the reference's saxpy example, 1 KiB per
+ * transfer: 0.78 against 0.62 ms; the stencil kernel: 3 %; the bandwidth-bound kernels: equal). */
 __device__ __forceinline__ void mbar_arrive_warp(uint32_t bar) {
-#ifdef CUDADMA_PER_THREAD_ARRIVE
+#ifndef CUDADMA_WARP_AGGREGATED_ARRIVE
   mbar_arrive(bar);
 #else
   const unsigned mask = __activemask();
@@ -388,6 +390,11 @@ class CudaDMA {
     m_phase ^= 1u;
     cudadma_b200::ptx::fence_proxy_async();
   }
+  /* the same wait for DMA threads that will fill the buffer with ordinary stores: no proxy fence */
+  __device__ __forceinline__ void wait_for_dma_start_for_stores(void) const {
+    cudadma_b200::detail::bounded_wait(m_bar_empty, m_phase, m_code | 1u);
+    m_phase ^= 1u;
+  }
   /* DMA threads: this thread's share of the transfer is complete (or tracked by the barrier) */
   __device__ __forceinline__ void finish_async_dma(void) const { cudadma_b200::ptx::mbar_arrive_warp(m_bar_full); }
 
@@ -511,6 +518,28 @@ __device__ __forceinline__ int issue_contiguous(const char *src, char *dst, cons
   return issue_rows<WS, LOAD_QUAL>(a, 1, bytes, ends | (unsigned long long)bytes, tid, nthreads, bar_full);
 }
 
+/* Small warp-specialised loads are latency-bound: the copy may only start once the compute threads
+ * have released the buffer, and then pays a full trip to DRAM. start_xfer_async() (which runs
+ * before that wait) therefore asks for the source to be brought into L2 meanwhile, so that the
+ * copy itself is an L2 hit (the reference's strided saxpy example, three rows of 1 KiB per
+ * transfer: 1.80 -> 1.41 ms). Only for transfers of at most CUDADMA_SMALL_PREFETCH_BYTES in at
+ * most CUDADMA_SMALL_PREFETCH_ROWS rows: larger ones are bandwidth-bound and run several buffers
+ * deep anyway, and a prefetch per row of a many-row window doubles the DMA threads' work (a
+ * 24-row stencil window lost 30 % with it). */
+#ifndef CUDADMA_SMALL_PREFETCH_BYTES
+#define CUDADMA_SMALL_PREFETCH_BYTES 4096
+#endif
+#ifndef CUDADMA_SMALL_PREFETCH_ROWS
+#define CUDADMA_SMALL_PREFETCH_ROWS 4
+#endif
+__device__ __forceinline__ void prefetch_small(const char *src, const int rows, const int row_bytes,
+                                               const long long src_stride, const int tid, const int nthreads) {
+  if (CUDADMA_SMALL_PREFETCH_BYTES <= 0 || rows <= 0 || row_bytes < 16 || tid < 0 || tid >= nthreads) return;
+  if (rows > CUDADMA_SMALL_PREFETCH_ROWS || (long long)rows * row_bytes > CUDADMA_SMALL_PREFETCH_BYTES) return;
+  if (((addr_bits(src) | (unsigned long long)row_bytes | (unsigned long long)src_stride) & 15) || !__isGlobal(src)) return;
+  for (int r = tid; r < rows; r += nthreads) ptx::bulk_prefetch_l2(src + (long long)r * src_stride, (uint32_t)row_bytes);
+}
+
 /* Constructor arguments arrive as 0..8 ints whose meaning depends on the
  * template level; ArgList just holds them. */
 struct ArgList {
@@ -607,7 +636,7 @@ class CudaDMASequential : public CudaDMA {
     return p;
   }
   __device__ __forceinline__ CudaDMASequential(const Params &p, int)
-      : CudaDMA(p.dmaID, p.ndma, p.ncomp, p.start, DO_SYNC), m_bytes(p.bytes), m_src(0) {}
+      : CudaDMA(p.dmaID, p.ndma, p.ncomp, p.start, DO_SYNC), m_bytes(p.bytes), m_src(0), m_staged(false) {}
 
  public:
   template <typename... I>
@@ -619,18 +648,70 @@ class CudaDMASequential : public CudaDMA {
   CUDADMA_B200_XFER_OVERLOADS(const void *__restrict__ src_ptr, src_ptr)
 
  private:
+  /* Small, fully templated, warp-specialised loads (at most 64 bytes per DMA thread) are staged the
+   * way the reference stages everything (cudaDMAv2.h:1461-1475): the DMA threads read the source
+   * into registers in start_xfer_async(), i.e. before they wait for the buffer, and store to shared
+   * memory after the wait. Such loops are latency chains -- compute releases, DMA fills, compute
+   * consumes -- and a copy that only starts after the release costs a second memory round trip per
+   * link (measured on the reference's saxpy example, 1 KiB per transfer: 0.39 us per iteration
+   * against 0.19). Larger transfers keep the asynchronous copies. */
+  static constexpr int PRE_UNITS =
+      (DO_SYNC && LEVEL == 3 && BYTES_PER_ELMT % 16 == 0 && BYTES_PER_ELMT <= 64 * (DMA_THREADS > 0 ? DMA_THREADS : 1))
+          ? (BYTES_PER_ELMT / 16 + (DMA_THREADS > 0 ? DMA_THREADS : 1) - 1) / (DMA_THREADS > 0 ? DMA_THREADS : 1)
+          : 0;
   template <bool GLOBAL, int LQ>
-  __device__ __forceinline__ void start_impl(const void *src) { m_src = static_cast<const char *>(src); }
+  __device__ __forceinline__ void start_impl(const void *src) {
+    m_src = static_cast<const char *>(src);
+    m_staged = false;
+#ifndef CUDADMA_NO_REGISTER_STAGING
+    if (PRE_UNITS > 0 && GLOBAL && m_is_dma_thread &&
+        (cudadma_b200::detail::addr_bits(src) & 15) == 0 && __isGlobal(src)) {
+#pragma unroll
+      for (int u = 0; u < (PRE_UNITS > 0 ? PRE_UNITS : 1); ++u) {
+        const int off = 16 * (m_dma_tid + u * (DMA_THREADS > 0 ? DMA_THREADS : 1));
+        if (off < BYTES_PER_ELMT) {
+          const uint4 *g = reinterpret_cast<const uint4 *>(m_src + off);
+          m_stage[u] = (LQ == LOAD_CACHE_ALL) ? *g : __ldcg(g);
+        }
+      }
+      m_staged = true;
+      return;
+    }
+#endif
+    if (DO_SYNC && GLOBAL) cudadma_b200::detail::prefetch_small(m_src, 1, m_bytes, 0, m_dma_tid, m_num_dma_threads);
+  }
   template <int LQ>
   __device__ __forceinline__ void finish_impl(void *dst) {
-    if (DO_SYNC) wait_for_dma_start();
+    if (PRE_UNITS > 0 && m_staged) wait_for_dma_start_for_stores();
+    else if (DO_SYNC) wait_for_dma_start();
     else if (!m_is_dma_thread) return;
+    if (PRE_UNITS > 0 && m_staged) {
+      /* all DMA threads of the object take the same branch: the test is on the two pointers only */
+      char *d = static_cast<char *>(dst);
+      const bool direct = (cudadma_b200::detail::addr_bits(dst) & 15) == 0;
+#pragma unroll
+      for (int u = 0; u < (PRE_UNITS > 0 ? PRE_UNITS : 1); ++u) {
+        const int off = 16 * (m_dma_tid + u * (DMA_THREADS > 0 ? DMA_THREADS : 1));
+        if (off < BYTES_PER_ELMT) {
+          if (direct) {
+            *reinterpret_cast<uint4 *>(d + off) = m_stage[u];
+          } else {
+            unsigned int *w = reinterpret_cast<unsigned int *>(d + off);
+            w[0] = m_stage[u].x; w[1] = m_stage[u].y; w[2] = m_stage[u].z; w[3] = m_stage[u].w;
+          }
+        }
+      }
+      finish_async_dma();
+      return;
+    }
     const int pending = cudadma_b200::detail::issue_contiguous<DO_SYNC, LQ>(
         m_src, static_cast<char *>(dst), m_bytes, m_dma_tid, m_num_dma_threads, m_bar_full);
     cudadma_b200::detail::complete<DO_SYNC>(pending, m_bar_full);
   }
   const int m_bytes;
   const char *m_src;
+  uint4 m_stage[PRE_UNITS > 0 ? PRE_UNITS : 1];
+  bool m_staged;
 };
 
 /* Host-side description of what a parameter set turns into on this
@@ -748,7 +829,11 @@ class CudaDMAStrided : public CudaDMA {
 
  private:
   template <bool GLOBAL, int LQ>
-  __device__ __forceinline__ void start_impl(const void *src) { m_src = static_cast<const char *>(src); }
+  __device__ __forceinline__ void start_impl(const void *src) {
+    m_src = static_cast<const char *>(src);
+    if (DO_SYNC && GLOBAL)
+      cudadma_b200::detail::prefetch_small(m_src, m_rows, m_bytes, m_src_stride, m_dma_tid, m_num_dma_threads);
+  }
   template <int LQ>
   __device__ __forceinline__ void finish_impl(void *dst) {
     using namespace cudadma_b200::detail;

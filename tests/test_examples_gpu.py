@@ -66,3 +66,45 @@ def test_reference_example_kernel_runs_unchanged_on_this_header(kid):
     border = ours.copy()
     border[R:R + dims[2], R:R + dims[1], R:R + dims[0]] = 0
     assert not border.any(), "wrote outside the grid"
+
+
+# ---- the v1-API saxpy examples (src/examples/saxpy, src/examples/saxpy_strided) ----
+V1_LIBS = {"sequential": ("libv1saxpy_ours.so", "libv1saxpy_ref.so"),
+           "strided": ("libv1saxpy_strided_ours.so", "libv1saxpy_strided_ref.so")}
+
+
+def run_saxpy(path, kernel_id, x, y, a):
+    lib = ctypes.CDLL(path)
+    lib.v1saxpy_elements.restype = ctypes.c_longlong
+    lib.v1saxpy_run.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float,
+                                ctypes.POINTER(ctypes.c_float)]
+    assert lib.v1saxpy_elements() == x.size
+    out = y.copy()
+    ms = ctypes.c_float(0)
+    err = lib.v1saxpy_run(kernel_id, out.ctypes.data, x.ctypes.data, a, ctypes.byref(ms))
+    assert err == 0, "cudaError %d" % err
+    return out, ms.value
+
+
+@pytest.mark.parametrize("kernel_id", [0, 1])
+@pytest.mark.parametrize("example", ["sequential", "strided"])
+def test_reference_v1_saxpy_example_runs_unchanged_on_this_header(example, kernel_id):
+    """saxpy_cudaDMA (kernel 0) and saxpy_cudaDMA_doublebuffer (kernel 1) of the reference's saxpy and
+    saxpy_strided examples, written against the v1 classes cudaDMASequential / cudaDMAStrided:
+    compiled unchanged against both headers (oracle/ref_v1_examples.cu), the two builds give the
+    same bits, and those are a * x + y."""
+    ours, ref = (os.path.join(ROOT, "oracle", "_ref", n) for n in V1_LIBS[example])
+    if not (os.path.exists(ours) and os.path.exists(ref)):
+        pytest.skip("v1 example libraries not built")
+    lib = ctypes.CDLL(ours)
+    lib.v1saxpy_elements.restype = ctypes.c_longlong
+    n = lib.v1saxpy_elements()
+    x = oracle.fill_uniform(n, 0x5A0 + kernel_id, 0.0, 1.0)
+    y = oracle.fill_uniform(n, 0x5B0 + kernel_id, 0.0, 1.0)
+    a = 0.84018773
+    got, ms_ours = run_saxpy(ours, kernel_id, x, y, a)
+    want, ms_ref = run_saxpy(ref, kernel_id, x, y, a)
+    print("v1 %s saxpy kernel %d: %.3f ms on this header, %.3f ms on the reference header" % (example, kernel_id, ms_ours, ms_ref))
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    exact = np.float64(np.float32(a)) * x.astype(np.float64) + y.astype(np.float64)
+    assert np.allclose(got, exact, rtol=1e-6, atol=0.0)
