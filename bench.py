@@ -103,12 +103,19 @@ class ClockSampler:
         return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
+HOST_CORES = None  # the cores this rank was bound to (N > 1 only)
+
+
 def setup_dist(n_gpus):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
+    global HOST_CORES
     if world > 1:
+        # N ranks copy to and from N GPUs at once: keep each rank's threads and pinned buffers in its GPU's NUMA node
+        from cudadma_b200.sharded import bind_host_thread_near_gpu
+        HOST_CORES = bind_host_thread_near_gpu(local)
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         # NCCL prints its version banner on stdout at the VERSION level; stdout carries the JSON line only
         if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
@@ -614,6 +621,9 @@ def main():
     if impl == "ours":
         # launches of this library per timed step: one kernel at N = 1, three (two boundary runs + interior) at N > 1
         # p2p: wait kernel, stencil kernel, signal kernel; nccl: two boundary launches and the interior launch
+        if world > 1:
+            line["config"]["host_threads"] = ("each rank bound to the %d cores NVML lists for its GPU" % len(HOST_CORES)) if HOST_CORES \
+                else "not bound (no NVML core list)"
         line["gpu_launches"] = args.steps * (1 if world == 1 else 3)
         line["launches_total_this_process"] = cd.launch_count() - before
     else:

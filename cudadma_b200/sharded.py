@@ -62,6 +62,35 @@ def slab_bounds(nz, world, rank, weights=None, min_planes=1):
     return cuts[rank], cuts[rank + 1]
 
 
+def bind_host_thread_near_gpu(device_index):
+    """Restricts the calling process to the CPU cores next to GPU `device_index` (the set NVML
+    reports for it), so that host buffers allocated and touched afterwards land in that GPU's
+    NUMA node and its PCIe copies do not cross the socket interconnect. Only this process's own
+    scheduling mask changes; nothing of the GPU is set. Returns the core list, or None where NVML
+    or the affinity call is not available (the process then stays as it was)."""
+    import os
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        handle = None
+        try:  # by PCI address: the CUDA index need not be NVML's when CUDA_VISIBLE_DEVICES is set
+            p = torch.cuda.get_device_properties(int(device_index))
+            handle = pynvml.nvmlDeviceGetHandleByPciBusId(
+                ("%08x:%02x:%02x.0" % (p.pci_domain_id, p.pci_bus_id, p.pci_device_id)).encode())
+        except Exception:
+            handle = pynvml.nvmlDeviceGetHandleByIndex(int(device_index))
+        words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(handle, words)
+        cores = [64 * w + b for w, m in enumerate(mask) for b in range(64) if (int(m) >> b) & 1]
+        allowed = sorted(set(cores) & set(os.sched_getaffinity(0)))
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return allowed
+    except Exception:
+        return None
+
+
 def _cuda_step(out, inp, nx, ny, nz_total, z_begin, z_end, coeff):
     capi.stencil25_step(out, inp, nx, ny, nz_total, z_begin, z_end, coeff)
 
