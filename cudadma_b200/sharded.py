@@ -154,6 +154,7 @@ class ShardedStencil:
             self.nxt = torch.zeros_like(self.cur)
         self.comm_stream = torch.cuda.Stream(device=self.device) if self.on_cuda and self.world > 1 else None
         self.steps_done = 0
+        self._copy_streams = None
 
     # -- data in and out ---------------------------------------------------
     def owned(self, buf=None):
@@ -280,9 +281,12 @@ class ShardedStencil:
         self.load(torch.from_numpy(planes.copy()))
         self.steps_done = int(head[5])
 
-    def run_host(self, h_out, h_in, steps):
+    def run_host(self, h_out, h_in, steps, overlap=None, chunk_planes=None):
         """The whole job from and to host memory (pinned tensors copy fastest): upload the slab,
         `steps` steps, download the slab. Returns when h_out holds the result.
+        overlap: on several ranks, overlap the three phases (see _run_host_overlapped); None = where
+        the slab is deep enough for it to pay (and the step function is this library's kernel).
+        chunk_planes: planes per upload piece of the overlapped form (None = 128 MiB pieces).
 
         On a single GPU with this library's kernel the call is cudadma_stencil25_run_host, which
         overlaps the upload, the steps and the download in pieces (same bits); the field held by
@@ -291,10 +295,126 @@ class ShardedStencil:
             with torch.cuda.device(self.device):
                 capi.stencil25_run_host(h_out, h_in, self.nx, self.ny, self.nz, steps, self.coeff)
             return
-        self.load(h_in)
-        self.run(steps)
-        self.store(h_out)
+        if self.world > 1 and overlap is None:
+            overlap = self.step_fn is _cuda_step and self.nzl >= 4 * steps + 2 * self._chunk_planes(None)
+        if self.world > 1 and overlap and steps > 0:
+            self._run_host_overlapped(h_out, h_in, steps, self._chunk_planes(chunk_planes))
+        else:
+            self.load(h_in)
+            self.run(steps)
+            self.store(h_out)
         if self.on_cuda:
             torch.cuda.current_stream(self.device).synchronize()
             if capi.device_status() != 0:
                 raise capi.CudaDMAError("ShardedStencil.run_host", capi.ERR_TIMEOUT, "a wait inside a kernel gave up")
+
+    def _chunk_planes(self, chunk_planes):
+        if chunk_planes:
+            return int(chunk_planes)
+        return max(8, min((128 << 20) // (self.plane * 4), self.nzl // 8))
+
+    def _run_host_overlapped(self, h_out, h_in, steps, chunk):
+        """Upload, steps and download of a slab overlapped, on several ranks.
+
+        A rank walks its slab in one direction, even ranks upwards and odd ranks downwards, so that
+        the two ranks at an interface either both begin there or both end there. Planes are uploaded
+        in that order; after `done[0]` of them have arrived, step t can produce the first
+        done[0] - 4t planes of the walk, and once the whole slab is up every step runs on to the far
+        end. Planes of a z-neighbour are needed in two places only: at an interface where both walks
+        begin, the first four planes of step t-1 are exchanged before either side starts step t
+        (early in the run, one small exchange per step); at an interface where both walks end, the
+        last four planes of step t-1 are exchanged once both sides have finished that step (at the
+        very end). Two ping-pong arrays suffice for the same reason as on one GPU (step t only
+        overwrites planes that step t-1 has finished reading). Every plane is computed by the same
+        kernel on the same operands as in run(), so the result is the same, bit for bit."""
+        nzl, nx, ny, nzt = self.nzl, self.nx, self.ny, self.nzl + 2 * R
+        up = self.rank % 2 == 0                        # direction of the walk
+        lower, upper = self.rank > 0, self.rank < self.world - 1
+        start_peer = (self.rank - 1 if lower else None) if up else (self.rank + 1 if upper else None)
+        end_peer = (self.rank + 1 if upper else None) if up else (self.rank - 1 if lower else None)
+        self.cur.zero_()
+        self.nxt.zero_()
+        buf = [self.cur, self.nxt]
+        h_in = h_in.reshape(nzl, ny, nx)
+        h_out = h_out.reshape(nzl, ny, nx)
+
+        def owned_range(s0, s1):
+            """walk positions [s0, s1) as a range of owned planes [a, b)"""
+            return (s0, s1) if up else (nzl - s1, nzl - s0)
+
+        def planes(b, a0, a1):
+            """owned planes [a0, a1) of array b, with the x/y border the step function may want"""
+            return buf[b].view(nzt, self.py, self.px)[R + a0:R + a1]
+
+        def inner(t):
+            return t[:, self.pad:self.pad + ny, self.pad:self.pad + nx]
+
+        def exchange(peer, b, at_start):
+            """Swap four boundary planes of array b with `peer`: mine go into its ghost planes, its
+            into mine. at_start: the interface is where this rank's walk begins."""
+            low_side = (at_start and up) or (not at_start and not up)   # the interface is below this slab
+            mine = self._planes(buf[b], R, R) if low_side else self._planes(buf[b], nzl, R)
+            ghost = self._planes(buf[b], 0, R) if low_side else self._planes(buf[b], R + nzl, R)
+            ops = [dist.P2POp(dist.isend, mine, peer, self.group), dist.P2POp(dist.irecv, ghost, peer, self.group)]
+            self._wait(dist.batch_isend_irecv(ops))
+
+        if self.on_cuda:
+            main = torch.cuda.current_stream(self.device)
+            if self._copy_streams is None:
+                self._copy_streams = (torch.cuda.Stream(device=self.device), torch.cuda.Stream(device=self.device))
+            s_up, s_down = self._copy_streams
+            s_up.wait_stream(main)
+            s_down.wait_stream(main)
+        done = [0] * (steps + 1)   # done[t]: the first done[t] planes of the walk hold the field after t steps
+        started = 0                # exchanges made at the interface where the walk begins (steps 0 .. started-1)
+        ended = 0                  # the same for the interface where it ends
+        down = 0                   # planes of the walk already on their way to the host
+        while done[steps] < nzl:
+            if done[0] < nzl:
+                s0, s1 = done[0], min(nzl, done[0] + chunk)
+                a0, a1 = owned_range(s0, s1)
+                if self.on_cuda:
+                    with torch.cuda.stream(s_up):
+                        inner(planes(0, a0, a1)).copy_(h_in[a0:a1], non_blocking=True)
+                    main.wait_stream(s_up)
+                else:
+                    inner(planes(0, a0, a1)).copy_(h_in[a0:a1])
+                done[0] = s1
+            for t in range(1, steps + 1):
+                src, dst = (t - 1) % 2, t % 2
+                if done[t] == 0 and start_peer is not None and started < t:
+                    if done[t - 1] < R:
+                        break
+                    exchange(start_peer, src, True)
+                    started = t
+                if done[t - 1] == nzl:
+                    if end_peer is not None and ended < t:
+                        exchange(end_peer, src, False)
+                        ended = t
+                    reach = nzl
+                else:
+                    reach = done[t - 1] - R
+                if reach <= done[t]:
+                    break
+                a0, a1 = owned_range(done[t], reach)
+                self.step_fn(buf[dst], buf[src], nx, ny, nzt, R + a0, R + a1, self.coeff)
+                done[t] = reach
+            if done[steps] > down:
+                a0, a1 = owned_range(down, done[steps])
+                if self.on_cuda:
+                    s_down.wait_stream(main)
+                    with torch.cuda.stream(s_down):
+                        h_out[a0:a1].copy_(inner(planes(steps % 2, a0, a1)), non_blocking=True)
+                else:
+                    h_out[a0:a1].copy_(inner(planes(steps % 2, a0, a1)))
+                down = done[steps]
+        if self.on_cuda:
+            main.wait_stream(s_down)
+        # leave the object holding the final field, as run() would
+        if steps % 2:
+            if self.slab is not None:
+                self.cur.copy_(self.nxt)   # the library's arrays keep their roles
+            else:
+                self.cur, self.nxt = self.nxt, self.cur
+        self._exchange(self.cur, wait=True)   # ghost planes of the final field, so that step() can go on from here
+        self.steps_done = steps

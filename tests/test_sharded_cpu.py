@@ -184,3 +184,49 @@ def test_checkpoint_restart_continues_bit_for_bit(tmp_path):
         assert p.exitcode == 0
     for rank, resumed_at, steps_done, same, refused in got:
         assert resumed_at == 2 and steps_done == 4 and same and refused, (rank, resumed_at, steps_done, same, refused)
+
+
+def _overlap_worker(rank, world, port, nz, steps, chunk, weights, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        nx, ny = 16, 12
+        field = oracle.fill_uniform(nx * ny * nz, 0xC4, 0.0, 1.0).reshape(nz, ny, nx)
+        st = sharded.ShardedStencil(nx, ny, nz, COEFF, device="cpu", step_fn=oracle_step, weights=weights)
+        h_in = torch.from_numpy(field[st.z_lo:st.z_hi].copy())
+        plain = torch.full_like(h_in, float("nan"))
+        st.run_host(plain, h_in, steps, overlap=False)
+        over = torch.full_like(h_in, float("nan"))
+        st.run_host(over, h_in, steps, overlap=True, chunk_planes=chunk)
+        same = bool(np.array_equal(plain.numpy().view(np.uint32), over.numpy().view(np.uint32)))
+        # the object holds the final field afterwards: one more step from it equals steps + 1 plain steps
+        more = st.run(1).numpy().copy()
+        ref = sharded.ShardedStencil(nx, ny, nz, COEFF, device="cpu", step_fn=oracle_step, weights=weights)
+        ref.load(h_in)
+        want = ref.run(steps + 1).numpy()
+        q.put((rank, same, bool(np.array_equal(more.view(np.uint32), want.view(np.uint32))), st.steps_done))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,nz,steps,chunk,weights", [(2, 40, 3, 4, None), (2, 33, 2, 1, None), (3, 61, 4, 5, None),
+                                                          (3, 48, 5, 100, None), (4, 70, 3, 3, (1.0, 1.6, 0.8, 1.2)),
+                                                          (2, 16, 1, 2, None)])
+def test_overlapped_host_run_on_several_ranks_is_the_plain_run(world, nz, steps, chunk, weights):
+    """Upload, steps and download overlapped on N ranks (even ranks walk up, odd ranks down, boundary
+    planes exchanged per step where two walks begin or end): the same bits as upload / run / download,
+    for pieces from one plane to more than a slab, equal and unequal slabs."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_overlap_worker, args=(r, world, port, nz, steps, chunk, weights, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, same, continues, steps_done in got:
+        assert same, "rank %d: overlapped run differs from the plain run" % rank
+        assert continues and steps_done == steps + 1, "rank %d: state after the overlapped run" % rank

@@ -69,3 +69,61 @@ def test_two_gpus_equal_one_gpu(nz, steps, exchange, weights):
         assert np.array_equal(got.view(np.uint32), one[lo:hi].view(np.uint32)), "rank %d differs" % rank
     exp = oracle.stencil25_f64(field.reshape(nz, ny, nx), cd.STENCIL_COEFFS, steps)
     assert np.abs(one - exp).max() / np.abs(exp).max() <= 1e-5
+
+
+def _host_worker(rank, world, port, nx, ny, nz, steps, exchange, chunk, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from cudadma_b200.sharded import ShardedStencil
+        from oracle import oracle
+        import cudadma_b200 as cd
+        field = oracle.fill_uniform(nx * ny * nz, 0xC4, 0.0, 1.0).reshape(nz, ny, nx)
+        st = ShardedStencil(nx, ny, nz, exchange=exchange)
+        h_in = torch.from_numpy(field[st.z_lo:st.z_hi].copy()).pin_memory()
+        plain = torch.full_like(h_in, float("nan")).pin_memory()
+        over = torch.full_like(h_in, float("nan")).pin_memory()
+        st.run_host(plain, h_in, steps, overlap=False)
+        st.run_host(over, h_in, steps, overlap=True, chunk_planes=chunk)
+        more = st.run(1).cpu().numpy().copy()   # the object goes on from the final field
+        torch.cuda.synchronize()
+        assert cd.device_status() == 0, "a bounded wait gave up on rank %d" % rank
+        dist.barrier()
+        q.put((rank, st.z_lo, st.z_hi, plain.numpy().copy(), over.numpy().copy(), more))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("nz,steps,exchange,chunk", [(96, 4, "nccl", 8), (64, 3, "p2p", 5), (40, 2, "p2p", 64)])
+def test_two_gpus_overlapped_host_run_is_the_plain_run(nz, steps, exchange, chunk):
+    """run_host with upload, steps and download overlapped on two GPUs: the same bits as the plain
+    sequence and as one GPU, and the object continues correctly from the final field."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two CUDA devices")
+    import cudadma_b200 as cd
+    from oracle import oracle
+    nx, ny, world = 128, 64, 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_host_worker, args=(r, world, port, nx, ny, nz, steps, exchange, chunk, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    parts = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    field = oracle.fill_uniform(nx * ny * nz, 0xC4, 0.0, 1.0)
+    a = torch.from_numpy(field).cuda()
+    b = torch.zeros_like(a)
+    one = cd.stencil25_run(a, b, nx, ny, nz, steps).cpu().numpy().reshape(nz, ny, nx).copy()
+    a = torch.from_numpy(field).cuda()
+    b = torch.zeros_like(a)
+    one_more = cd.stencil25_run(a, b, nx, ny, nz, steps + 1).cpu().numpy().reshape(nz, ny, nx)
+    for rank, lo, hi, plain, over, more in parts:
+        assert np.array_equal(plain.view(np.uint32), one[lo:hi].view(np.uint32)), "rank %d: plain host run" % rank
+        assert np.array_equal(over.view(np.uint32), one[lo:hi].view(np.uint32)), "rank %d: overlapped host run" % rank
+        assert np.array_equal(more.view(np.uint32), one_more[lo:hi].view(np.uint32)), "rank %d: next step" % rank
