@@ -459,6 +459,11 @@ def run_stencil_job(impl, args, rank, world, local, peak, peak_kind):
                     "cudadma_stencil25_run_host: pinned host field up in 128 MiB pieces, %d steps trailing the "
                     "upload, finished planes down, all overlapped; bytes divided by the steps" % args.steps)
                    if (world == 1 and impl == "ours") else
+                   ("whole job through ShardedStencil.run_host, overlapped form: every rank uploads its pinned slab "
+                    "in pieces while its %d steps trail the upload and finished planes go back; even ranks walk "
+                    "their slab upwards, odd ranks downwards, boundary planes exchanged per step where two walks "
+                    "begin or end; bytes are per rank, divided by the steps" % args.steps)
+                   if impl == "ours" else
                    ("whole job through ShardedStencil.run_host: the slab is uploaded once, stepped %d times and "
                     "downloaded once; bytes are per rank, divided by the steps" % args.steps),
            "seconds": round(e2e_s, 4)}
