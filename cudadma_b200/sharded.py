@@ -15,13 +15,19 @@ One step, exchange = "nccl":
      send/recv: NCCL over NVLink on GPUs) on a side stream;
   3. the remaining interior planes are computed meanwhile on the main stream;
   4. the main stream joins the exchange, buffers swap.
-One step, exchange = "p2p" (CUDA devices only): the boundary kernel itself stores
-every result twice, into this rank's array and into the neighbour's ghost planes
-over NVLink (the arrays are shared between the processes with CUDA IPC), and a
-flag word per neighbour says how many steps each side has finished; see
-cudadma_slab_step in include/cudadma_b200.h. No collective library on the step.
+One step, exchange = "p2p" (CUDA devices only): one kernel launch computes all
+owned planes and stores the first and last four a second time, into the
+neighbours' ghost planes over NVLink (the arrays are shared between the
+processes with CUDA IPC), and a flag word per neighbour says how many steps each
+side has finished; see cudadma_slab_step in include/cudadma_b200.h. No
+collective library on the step.
 Every plane is computed by the same kernel with the same arithmetic whatever
 the sharding, so an N-rank run reproduces the 1-rank field bit for bit.
+
+Around the step: slabs cut in proportion to the ranks' speeds (weights), a
+host-side deadline on the exchange (exchange_timeout), checkpoint / restart of a
+rank's slab (save / restore), and run_host, the whole job from and to host
+memory with upload, steps and download overlapped.
 """
 import datetime
 
