@@ -61,6 +61,15 @@ def build_apitest(force=False):
     return target
 
 
+def build_checked_probe(force=False):
+    """One small kernel against the -DCUDADMA_CHECKED build of the header (tests/csrc/checked_probe.cu)."""
+    target = os.path.join(ROOT, "tests", "csrc", "libcudadma_checked_probe.so")
+    srcs = [os.path.join(ROOT, "tests", "csrc", "checked_probe.cu")] + _glob("include/cudadma")
+    if force or _newer(target, srcs):
+        _run([NVCC] + NVCC_FLAGS + ["-Iinclude/cudadma", "-o", target, "tests/csrc/checked_probe.cu"])
+    return target
+
+
 def build_oracle(force=False):
     target = os.path.join(ROOT, "oracle", "liboracle.so")
     srcs = [os.path.join(ROOT, "oracle", "oracle.c")]
@@ -78,7 +87,7 @@ def build_reference(force=False):
 
 
 def build_all(force=False, reference=True):
-    out = [build_library(force), build_apitest(force), build_oracle(force)]
+    out = [build_library(force), build_apitest(force), build_checked_probe(force), build_oracle(force)]
     if reference:
         out.append(build_reference(force))
     return out

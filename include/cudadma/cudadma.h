@@ -75,6 +75,82 @@ static inline __host__ cudaError_t read_status(unsigned int *out, cudaStream_t s
   return e;
 }
 
+/*
+ * -DCUDADMA_CHECKED: a debugging build for machines without a memory checker. The caller names the
+ * ranges of global memory that transfers may touch (checked::set_windows, up to eight); every
+ * transfer of the engine then tests each run of bytes it is about to move -- global addresses
+ * against those ranges, shared addresses against the CTA's shared-memory size -- and a transfer
+ * with a run outside is not issued at all: the first such run is recorded (checked::read_violation)
+ * and the status word gets the code 0x8000B000 | dmaID-less kind (1 source, 2 destination), the
+ * handshake completes as usual, and the kernel runs on with a buffer that was not filled instead
+ * of faulting. Tensor-map transfers are bounded by their map and are not tested.
+ */
+#ifdef CUDADMA_CHECKED
+namespace checked {
+struct Windows { unsigned long long lo[8], hi[8]; int n; };
+struct Violation { unsigned long long address, bytes; unsigned int kind, block, thread, pad; };
+static __device__ Windows g_windows = {{0}, {0}, 0};
+static __device__ Violation g_violation = {0, 0, 0, 0, 0, 0};
+
+/* bases[i] .. bases[i] + bytes[i] are the ranges of global memory a transfer may read or write */
+static inline __host__ cudaError_t set_windows(const void *const *bases, const size_t *bytes, int n,
+                                               cudaStream_t stream = 0) {
+  Windows w;
+  if (n < 0 || n > 8) return cudaErrorInvalidValue;
+  for (int i = 0; i < 8; ++i) {
+    w.lo[i] = i < n ? (unsigned long long)reinterpret_cast<uintptr_t>(bases[i]) : 0ull;
+    w.hi[i] = i < n ? w.lo[i] + bytes[i] : 0ull;
+  }
+  w.n = n;
+  cudaError_t e = cudaMemcpyToSymbolAsync(g_windows, &w, sizeof(w), 0, cudaMemcpyHostToDevice, stream);
+  return e != cudaSuccess ? e : cudaStreamSynchronize(stream);
+}
+/* reads and clears the record of the first refused run (kind 0 = none) */
+static inline __host__ cudaError_t read_violation(Violation *out, cudaStream_t stream = 0) {
+  const Violation none = {0, 0, 0, 0, 0, 0};
+  cudaError_t e = cudaMemcpyFromSymbolAsync(out, g_violation, sizeof(Violation), 0, cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  if (e == cudaSuccess && out->kind != 0)
+    e = cudaMemcpyToSymbolAsync(g_violation, &none, sizeof(none), 0, cudaMemcpyHostToDevice, stream);
+  return e;
+}
+__device__ __forceinline__ bool run_ok(const void *p, unsigned long long bytes) {
+  if (__isShared(p)) {
+    unsigned int total;
+    asm volatile("mov.u32 %0, %%total_smem_size;" : "=r"(total));
+    const unsigned long long off = (unsigned long long)__cvta_generic_to_shared(p);
+    return off + bytes <= total;
+  }
+  const unsigned long long a = (unsigned long long)reinterpret_cast<uintptr_t>(p);
+  for (int i = 0; i < g_windows.n; ++i)
+    if (a >= g_windows.lo[i] && a + bytes <= g_windows.hi[i]) return true;
+  return false;
+}
+__device__ __forceinline__ void record(const void *p, unsigned long long bytes, unsigned int kind) {
+  if (atomicCAS(&g_status_word, 0u, 0x8000B000u | kind) == 0u) {
+    g_violation.address = (unsigned long long)reinterpret_cast<uintptr_t>(p);
+    g_violation.bytes = bytes;
+    g_violation.block = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+    g_violation.thread = threadIdx.x;
+    g_violation.kind = kind;
+  }
+}
+/* true when every run of the transfer lies inside what it may touch; the calling thread tests the
+ * runs it would move itself and all threads of the transfer get the same answer only if they
+ * all pass -- so the test is made on ALL runs by every thread (debug build: cost is not a concern) */
+template <typename ROWS>
+__device__ __forceinline__ bool transfer_ok(const ROWS &a, int rows, int row_bytes) {
+  for (int r = 0; r < rows; ++r) {
+    const void *s = a.src_row(r);
+    const void *d = a.dst_row(r);
+    if (!run_ok(s, (unsigned long long)row_bytes)) { record(s, (unsigned long long)row_bytes, 1u); return false; }
+    if (!run_ok(d, (unsigned long long)row_bytes)) { record(d, (unsigned long long)row_bytes, 2u); return false; }
+  }
+  return true;
+}
+}  // namespace checked
+#endif
+
 namespace ptx {
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -438,6 +514,9 @@ __device__ __forceinline__ int issue_rows(const ROWS &a, const int rows, const i
   constexpr bool L2_ONLY = (LOAD_QUAL != LOAD_CACHE_ALL);
   constexpr bool EVICT_FIRST = (LOAD_QUAL == LOAD_CACHE_STREAMING) || (LOAD_QUAL == LOAD_CACHE_LAST_USE);
   if (rows <= 0 || row_bytes <= 0) return 0;
+#ifdef CUDADMA_CHECKED
+  if (!checked::transfer_ok(a, rows, row_bytes)) return 0;
+#endif
   const char *s0 = a.src_row(0);
   char *d0 = a.dst_row(0);
   const int unit = copy_unit(mask);
@@ -494,6 +573,12 @@ __device__ __forceinline__ int issue_contiguous(const char *src, char *dst, cons
                                                 const int nthreads, const uint32_t bar_full) {
   constexpr bool EVICT_FIRST = (LOAD_QUAL == LOAD_CACHE_STREAMING) || (LOAD_QUAL == LOAD_CACHE_LAST_USE);
   const unsigned long long ends = addr_bits(src) | addr_bits(dst);
+#ifdef CUDADMA_CHECKED
+  {
+    const StridedRows whole = {src, dst, 0, 0};
+    if (bytes > 0 && !checked::transfer_ok(whole, 1, bytes)) return 0;
+  }
+#endif
   if (WS && (ends & 15) == 0 && bytes >= CUDADMA_BULK_ROW_MIN && __isGlobal(src) && __isShared(dst)) {
     const int body = bytes & ~15;
     const int nwarps = (nthreads + 31) >> 5;
@@ -534,6 +619,9 @@ __device__ __forceinline__ int issue_contiguous(const char *src, char *dst, cons
 #endif
 __device__ __forceinline__ void prefetch_small(const char *src, const int rows, const int row_bytes,
                                                const long long src_stride, const int tid, const int nthreads) {
+#ifdef CUDADMA_CHECKED
+  return; /* nothing is touched before it has been tested */
+#endif
   if (CUDADMA_SMALL_PREFETCH_BYTES <= 0 || rows <= 0 || row_bytes < 16 || tid < 0 || tid >= nthreads) return;
   if (rows > CUDADMA_SMALL_PREFETCH_ROWS || (long long)rows * row_bytes > CUDADMA_SMALL_PREFETCH_BYTES) return;
   if (((addr_bits(src) | (unsigned long long)row_bytes | (unsigned long long)src_stride) & 15) || !__isGlobal(src)) return;
@@ -663,7 +751,7 @@ class CudaDMASequential : public CudaDMA {
   __device__ __forceinline__ void start_impl(const void *src) {
     m_src = static_cast<const char *>(src);
     m_staged = false;
-#ifndef CUDADMA_NO_REGISTER_STAGING
+#if !defined(CUDADMA_NO_REGISTER_STAGING) && !defined(CUDADMA_CHECKED) /* checked builds move everything through the engine */
     if (PRE_UNITS > 0 && GLOBAL && m_is_dma_thread &&
         (cudadma_b200::detail::addr_bits(src) & 15) == 0 && __isGlobal(src)) {
 #pragma unroll

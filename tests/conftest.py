@@ -37,6 +37,7 @@ def built_artifacts():
     from cudadma_b200 import build
     need = [os.path.join(ROOT, "cudadma_b200", "libcudadma_b200.so"),
             os.path.join(ROOT, "tests", "csrc", "libcudadma_apitest.so"),
+            os.path.join(ROOT, "tests", "csrc", "libcudadma_checked_probe.so"),
             os.path.join(ROOT, "oracle", "liboracle.so")]
     if not all(os.path.exists(p) for p in need):
         if shutil.which("nvcc") or os.path.exists(build.NVCC):
