@@ -45,6 +45,18 @@ def test_weighted_slab_bounds():
         sharded.slab_bounds(64, 2, 0, [1.0, 0.0], 8)
 
 
+def test_binding_near_a_gpu_is_harmless_without_one():
+    """Without NVML or a device the helper leaves the process as it was and says so."""
+    before = os.sched_getaffinity(0)
+    cores = sharded.bind_host_thread_near_gpu(0)
+    after = os.sched_getaffinity(0)
+    if cores is None:
+        assert after == before
+    else:
+        assert cores and set(cores) == set(after) and set(after) <= set(before)
+        os.sched_setaffinity(0, before)
+
+
 def test_refuses_to_run_without_cuda_or_step_function():
     if torch.cuda.is_available():
         pytest.skip("a CUDA device is present")
