@@ -217,16 +217,8 @@ int launch_stencil_native(float *out, const stencil25::Peers &peer, const float 
   const cuuint32_t box[3] = {stencil25::WIN_X, stencil25::WIN_Y, 1};
   if (int r = make_map_f32(&map, in, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, STENCIL25_L2PROMO)) return r;
   dim3 grid(tiles_x, tiles_y, zc);
-#ifdef STENCIL25_TMA_STORE
-  CUtensorMap omap;
-  const cuuint32_t obox[3] = {stencil25::TILE_X, stencil25::TILE_Y / 2, 1};
-  if (int r = make_map_f32(&omap, out, 3, dims, strides, obox, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE)) return r;
-  stencil25::tensor_kernel<<<grid, stencil25::COMPUTE_THREADS + stencil25::DMA_THREADS, stencil25::SMEM_BYTES, s>>>(
-      map, omap, out, peer, nx, ny, z_begin, z_end, z_chunk, k);
-#else
   stencil25::tensor_kernel<<<grid, stencil25::COMPUTE_THREADS + stencil25::DMA_THREADS, stencil25::SMEM_BYTES, s>>>(
       map, out, peer, nx, ny, z_begin, z_end, z_chunk, k);
-#endif
   return launched();
 }
 

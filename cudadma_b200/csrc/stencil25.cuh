@@ -43,14 +43,7 @@ constexpr int STAGES = STENCIL25_STAGES;
 static_assert(SLOTS % STAGES == 0, "the ring size must divide nine so that stage indices stay static");
 constexpr int PY = 2; /* rows of a thread's patch (the patch is four points wide) */
 constexpr int COMPUTE_THREADS = (TILE_X / 4) * (TILE_Y / PY), DMA_THREADS = 32;
-#ifdef STENCIL25_TMA_STORE
-/* results leave through shared memory: per compute warp two buffers of its 32 x 8 half of the tile */
-constexpr int OUT_HALF_BYTES = TILE_X * (TILE_Y / 2) * 4; /* 1024 */
-constexpr int OUT_BYTES = 2 /* warps */ * 2 /* buffers */ * OUT_HALF_BYTES;
-#else
-constexpr int OUT_BYTES = 0;
-#endif
-constexpr int SMEM_BYTES = STAGES * PLANE_BYTES + OUT_BYTES;
+constexpr int SMEM_BYTES = STAGES * PLANE_BYTES;
 
 struct Coeffs { float c[5]; };
 /* second destinations of the lowest and highest output planes (see tensor_kernel) */
@@ -149,8 +142,7 @@ __device__ __forceinline__ void fold_plane(const float *__restrict__ win, float2
 template <bool PUSH, typename RING>
 __device__ __forceinline__ void compute_side(RING &ring, const unsigned char *smem, float *__restrict__ out,
                                              const Peers &peer, const int nx, const int ny, const int x0,
-                                             const int y0, const int z0, const int depth, const Coeffs &k,
-                                             const CUtensorMap *out_map) {
+                                             const int y0, const int z0, const int depth, const Coeffs &k) {
   const int nplanes = depth + 2 * R;
   const int tx = threadIdx.x & 7, ty = threadIdx.x >> 3;
   const long long py = nx, pz = (long long)nx * ny;
@@ -179,46 +171,15 @@ __device__ __forceinline__ void compute_side(RING &ring, const unsigned char *sm
               /* output plane kp - 8 of this CTA is complete: it sits in slot (kk - 4) mod 9 */
               const float2(&r)[2][2] = acc[(kk + SLOTS - R) % SLOTS];
               const long long plane = (long long)(kp - 2 * R) * pz;
-#ifdef STENCIL25_TMA_STORE
-              {
-                /* this warp's half tile (rows 8w .. 8w+7) goes to one of its two buffers and from
-                 * there to global memory by one tensor store issued by lane 0; nothing but this warp
-                 * touches the buffers, so the warp synchronises with itself only */
-                const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-                const int ob = (kp - 2 * R) & 1;
-                unsigned char *obuf = const_cast<unsigned char *>(smem) + STAGES * PLANE_BYTES +
-                                      (warp * 2 + ob) * OUT_HALF_BYTES;
-                if (lane == 0) cudadma_b200::ptx::bulk_wait_read<1>(); /* the store two planes back has left this buffer */
-                __syncwarp();
-                float2 *orow = reinterpret_cast<float2 *>(obuf + ((PY * ty) & 7) * (TILE_X * 4) + 16 * tx);
-                const int first = ty & 1; /* neighbouring rows start with different halves: no bank conflict */
-                orow[first] = r[0][first];
-                orow[first ^ 1] = r[0][first ^ 1];
-                orow[TILE_X / 2 + first] = r[1][first];
-                orow[TILE_X / 2 + (first ^ 1)] = r[1][first ^ 1];
-                cudadma_b200::ptx::fence_proxy_async();
-                __syncwarp();
-                if (lane == 0) {
-                  cudadma_b200::ptx::tensor_s2g_3d(out_map, x0, y0 + 8 * warp, z0 + kp - 2 * R,
-                                                   cudadma_b200::ptx::smem_u32(obuf));
-                  cudadma_b200::ptx::bulk_commit();
-                }
-              }
-#else
               const float4 v0 = make_float4(r[0][0].x, r[0][0].y, r[0][1].x, r[0][1].y);
               const float4 v1 = make_float4(r[1][0].x, r[1][0].y, r[1][1].x, r[1][1].y);
               if (row0_ok) *reinterpret_cast<float4 *>(o + plane) = v0;
               if (row1_ok) *reinterpret_cast<float4 *>(o + plane + py) = v1;
-#endif
             }
           }
         },
         std::make_integer_sequence<int, SLOTS>{});
   }
-#ifdef STENCIL25_TMA_STORE
-  if ((threadIdx.x & 31) == 0) cudadma_b200::ptx::bulk_wait<0>(); /* this warp's stores have been performed */
-  __syncwarp();
-#endif
   if (PUSH) {
     /* Second destinations. Kept out of the plane loop, which is tight on registers: every thread
      * reads back the cells it has just stored itself (its own stores are visible to it, and
@@ -258,11 +219,7 @@ __global__ void __launch_bounds__(COMPUTE_THREADS + DMA_THREADS, STENCIL25_MIN_B
 #else
 __global__ void __launch_bounds__(COMPUTE_THREADS + DMA_THREADS)
 #endif
-tensor_kernel(const __grid_constant__ CUtensorMap in_map,
-#ifdef STENCIL25_TMA_STORE
-              const __grid_constant__ CUtensorMap out_map,
-#endif
-              float *__restrict__ out, const Peers peer,
+tensor_kernel(const __grid_constant__ CUtensorMap in_map, float *__restrict__ out, const Peers peer,
               const int nx, const int ny, const int z_begin, const int z_end, const int z_chunk, const Coeffs k) {
   extern __shared__ __align__(128) unsigned char smem[];
   typedef CudaDMAHalo<float, R, true, 16> Halo;
@@ -283,13 +240,8 @@ tensor_kernel(const __grid_constant__ CUtensorMap in_map,
     /* Only CTAs whose planes reach into a pushed range run the instantiation with the second
      * stores behind its loop (one body for all measured 1 % slower without peers). */
     const bool pushes = (peer.lo && z0 < peer.lo_end) || (peer.hi && z0 + depth > peer.hi_begin);
-#ifdef STENCIL25_TMA_STORE
-    const CUtensorMap *om = &out_map;
-#else
-    const CUtensorMap *om = nullptr;
-#endif
-    if (pushes) compute_side<true>(ring, smem, out, peer, nx, ny, x0, y0, z0, depth, k, om);
-    else compute_side<false>(ring, smem, out, peer, nx, ny, x0, y0, z0, depth, k, om);
+    if (pushes) compute_side<true>(ring, smem, out, peer, nx, ny, x0, y0, z0, depth, k);
+    else compute_side<false>(ring, smem, out, peer, nx, ny, x0, y0, z0, depth, k);
   }
 }
 #endif

@@ -288,12 +288,6 @@ __device__ __forceinline__ void tensor_s2g_2d(const CUtensorMap *map, int x, int
                "r"(x), "r"(y), "r"(src)
                : "memory");
 }
-__device__ __forceinline__ void tensor_s2g_3d(const CUtensorMap *map, int x, int y, int z, uint32_t src) {
-  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];" ::"l"(
-                   reinterpret_cast<uint64_t>(map)),
-               "r"(x), "r"(y), "r"(z), "r"(src)
-               : "memory");
-}
 /* per-thread asynchronous copy global -> shared of UNIT = 4, 8 or 16 bytes */
 template <int UNIT, bool L2_ONLY>
 __device__ __forceinline__ void ldgsts(uint32_t dst, const void *src) {
