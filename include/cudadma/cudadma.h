@@ -814,7 +814,12 @@ class CudaDMASequential<DO_SYNC, 0, 0, 0, 0> {
     const int warps = (DMA_THREADS + 31) / 32;
     fprintf(stdout, "CudaDMASequential on sm_100a: ALIGNMENT %d BYTES_PER_ELMT %d DMA_THREADS %d (%s)\n", ALIGNMENT,
             BYTES_PER_ELMT, DMA_THREADS, FULL_TEMPLATE ? "fully templated" : "runtime sized");
-    if (bulk)
+    const bool staged = FULL_TEMPLATE && (ALIGNMENT == 16) && (BYTES_PER_ELMT % 16 == 0) && DMA_THREADS > 0 &&
+                        (BYTES_PER_ELMT <= 64 * DMA_THREADS);
+    if (staged)
+      fprintf(stdout, "  warp-specialised: staged through registers, %d 16-byte loads per DMA thread before the wait, "
+                      "stores after it (small transfer)\n", (BYTES_PER_ELMT / 16 + DMA_THREADS - 1) / DMA_THREADS);
+    else if (bulk)
       fprintf(stdout, "  warp-specialised: %d bulk copies (cp.async.bulk) of up to %d bytes, tail %d bytes via registers\n",
               warps, ((BYTES_PER_ELMT & ~15) + warps - 1) / (warps > 0 ? warps : 1), BYTES_PER_ELMT & 15);
     else
@@ -822,7 +827,7 @@ class CudaDMASequential<DO_SYNC, 0, 0, 0, 0> {
               ALIGNMENT);
     fprintf(stdout, "  non-specialised : per-thread cp.async, %d copies per thread\n",
             DMA_THREADS > 0 ? (BYTES_PER_ELMT / ALIGNMENT + DMA_THREADS - 1) / DMA_THREADS : 0);
-    if (verbose) fprintf(stdout, "  BYTES_PER_THREAD %d is not used: no register staging\n", BYTES_PER_THREAD);
+    if (verbose) fprintf(stdout, "  BYTES_PER_THREAD %d is not used: staging, where it happens, is bounded by 64 bytes per thread\n", BYTES_PER_THREAD);
     fflush(stdout);
   }
 };
