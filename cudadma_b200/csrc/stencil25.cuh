@@ -212,13 +212,7 @@ __device__ __forceinline__ void compute_side(RING &ring, const unsigned char *sm
 #ifndef STENCIL25_MIN_BLOCKS
 #define STENCIL25_MIN_BLOCKS 4 /* four CTAs per SM need at most 170 registers; a fifth would spill */
 #endif
-#if defined(STENCIL25_MAXNREG)
-__global__ void __maxnreg__(STENCIL25_MAXNREG)
-#elif defined(STENCIL25_MIN_BLOCKS)
 __global__ void __launch_bounds__(COMPUTE_THREADS + DMA_THREADS, STENCIL25_MIN_BLOCKS)
-#else
-__global__ void __launch_bounds__(COMPUTE_THREADS + DMA_THREADS)
-#endif
 tensor_kernel(const __grid_constant__ CUtensorMap in_map, float *__restrict__ out, const Peers peer,
               const int nx, const int ny, const int z_begin, const int z_end, const int z_chunk, const Coeffs k) {
   extern __shared__ __align__(128) unsigned char smem[];
