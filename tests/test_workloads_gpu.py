@@ -308,3 +308,21 @@ def test_stencil_host_run_overlapped_is_the_plain_run(nx, ny, nz, steps, chunk):
     assert np.array_equal(h_in.numpy().view(np.uint32), exp.view(np.uint32))
     status_clean()
     assert rel_err(exp.reshape(nz, ny, nx), oracle.stencil25_f64(f.reshape(nz, ny, nx), cd.STENCIL_COEFFS, steps)) <= STENCIL_TOL
+
+
+def test_stencil_host_run_library_pieces_on_the_512_cube():
+    """The benchmark's single-GPU stencil (512^3, 10 steps) from and to pinned host memory with the
+    library's own piece size: the overlapped form is taken (four pieces of 128 planes) and gives
+    the bits of the device-resident run."""
+    nx = ny = nz = 512
+    steps = 10
+    h_in = torch.empty(nx * ny * nz, dtype=torch.float32).pin_memory()
+    h_in.copy_(torch.from_numpy(oracle.fill_uniform(nx * ny * nz, 0xC4, 0.0, 1.0)))
+    h_out = torch.full((nx * ny * nz,), float("nan")).pin_memory()
+    cd.stencil25_run_host(h_out, h_in, nx, ny, nz, steps)
+    d_a, d_b = h_in.cuda(), torch.zeros(nx * ny * nz, dtype=torch.float32, device="cuda")
+    cd.stencil25_run(d_a, d_b, nx, ny, nz, steps)
+    want = d_b if steps & 1 else d_a
+    assert torch.equal(h_out.cuda().view(torch.int32), want.view(torch.int32))
+    status_clean()
+    cd.release_workspace()
