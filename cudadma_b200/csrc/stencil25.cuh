@@ -54,7 +54,8 @@ struct Peers {
 
 /* Arithmetic is done two points at a time with the packed fp32 FMA of sm_100
  * (fma.rn.f32x2 through __ffma2_rn): one issue slot for two fused multiply-adds,
- * each bit-identical to fmaf. A patch row of four points is two such pairs. */
+ * each bit-identical to fmaf. A patch row of four points is two such pairs. The
+ * x neighbours at odd distances are the exception (see fold_plane): scalar fmaf. */
 struct Row { float2 p[2]; };
 
 __device__ __forceinline__ Row ld_row(const float *p) {
@@ -95,21 +96,31 @@ __device__ __forceinline__ void fold_plane(const float *__restrict__ win, float2
     }
   if (in_plane) {
     float2(&o)[2][2] = acc[KK % SLOTS];
-    /* x direction: row cells x-4 .. x+7 as pairs starting at even (e) and odd (q) offsets */
+    /* x direction: row cells x-4 .. x+7; e[] are the pairs that start at even cells */
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
       const Row l = ld_row(win + j * WIN_X - 4), r = ld_row(win + j * WIN_X + 4);
       const float2 e[6] = {l.p[0], l.p[1], u[j].p[0], u[j].p[1], r.p[0], r.p[1]};
-      float2 q[5];
-#pragma unroll
-      for (int t = 0; t < 5; ++t) q[t] = make_float2(e[t].y, e[t + 1].x);
+      const float cell[12] = {e[0].x, e[0].y, e[1].x, e[1].y, e[2].x, e[2].y,
+                              e[3].x, e[3].y, e[4].x, e[4].y, e[5].x, e[5].y};
 #pragma unroll
       for (int h = 0; h < 2; ++h)
 #pragma unroll
         for (int rr = 1; rr <= R; ++rr) {
           const int kl = 4 + 2 * h - rr, kr = 4 + 2 * h + rr; /* first cell of the left / right neighbour pair */
-          o[j][h] = __ffma2_rn(c2[rr], (kl & 1) ? q[kl >> 1] : e[kl >> 1], o[j][h]);
-          o[j][h] = __ffma2_rn(c2[rr], (kr & 1) ? q[kr >> 1] : e[kr >> 1], o[j][h]);
+          if (rr & 1) {
+            /* The pair starts at an odd cell, so it sits in no even-aligned register pair and a
+             * packed FMA would first need two moves to build its operand. Two scalar FMAs on the
+             * cells themselves give the same bits; leaving the five shuffled pairs out also takes ten
+             * registers out of the tightest part of the loop (measured: 6 to 9 % for the kernel). */
+            o[j][h].x = fmaf(c2[rr].x, cell[kl], o[j][h].x);
+            o[j][h].y = fmaf(c2[rr].y, cell[kl + 1], o[j][h].y);
+            o[j][h].x = fmaf(c2[rr].x, cell[kr], o[j][h].x);
+            o[j][h].y = fmaf(c2[rr].y, cell[kr + 1], o[j][h].y);
+          } else {
+            o[j][h] = __ffma2_rn(c2[rr], e[kl >> 1], o[j][h]);
+            o[j][h] = __ffma2_rn(c2[rr], e[kr >> 1], o[j][h]);
+          }
         }
     }
     /* y direction: own rows feed each other, the eight rows around the patch are streamed */
