@@ -45,7 +45,7 @@
 #define STENCIL25_L2PROMO CU_TENSOR_MAP_L2_PROMOTION_L2_256B
 #endif
 #ifndef STENCIL_CTAS_TARGET
-#define STENCIL_CTAS_TARGET 24 /* CTAs per SM the automatic z_chunk aims for */
+#define STENCIL_CTAS_TARGET 8 /* CTAs per SM the automatic z_chunk aims for (two are resident) */
 #endif
 
 #include "cudadma.h"
@@ -217,6 +217,13 @@ int launch_stencil_native(float *out, const stencil25::Peers &peer, const float 
   const cuuint32_t box[3] = {stencil25::WIN_X, stencil25::WIN_Y, 1};
   if (int r = make_map_f32(&map, in, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, STENCIL25_L2PROMO)) return r;
   dim3 grid(tiles_x, tiles_y, zc);
+  if (stencil25::SMEM_BYTES > 47 * 1024) {
+    static bool opted_in = false; /* dynamic shared memory above the default limit: asked for once */
+    if (!opted_in) {
+      if (int r = allow_smem(stencil25::tensor_kernel, stencil25::SMEM_BYTES)) return r;
+      opted_in = true;
+    }
+  }
   stencil25::tensor_kernel<<<grid, stencil25::COMPUTE_THREADS + stencil25::DMA_THREADS, stencil25::SMEM_BYTES, s>>>(
       map, out, peer, nx, ny, z_begin, z_end, z_chunk, k);
   return launched();

@@ -3,10 +3,10 @@
  *   out = c0*u + sum_{r=1..4} c_r*(u[x-r]+u[x+r]+u[y-r]+u[y+r]+u[z-r]+u[z+r]),
  * zero outside the grid, as a z-marching kernel fed by CudaDMAHalo objects.
  *
- * One CTA owns a 32 x 16 xy tile and a run of z planes. Its DMA warp streams
- * the tile plus its radius-4 halo (40 x 24 floats, one TMA box per plane, zero
+ * One CTA owns a 32 x 32 xy tile and a run of z planes. Its DMA warp streams
+ * the tile plus its radius-4 halo (40 x 40 floats, one TMA box per plane, zero
  * fill outside the grid) into a ring of shared-memory buffers. The compute
- * threads (64) each own a 4 (x) by 2 (y) patch of the tile. Every plane is read from
+ * threads (128) each own a 4 (x) by 2 (y) patch of the tile. Every plane is read from
  * shared memory exactly once, when it arrives, and is pushed forward into the
  * nine output planes it contributes to:
  *   - its in-plane (x and y) neighbours go to the output plane of the same z;
@@ -32,9 +32,12 @@
 namespace stencil25 {
 
 constexpr int R = 4;
-constexpr int TILE_X = 32, TILE_Y = 16;
-constexpr int WIN_X = TILE_X + 2 * R, WIN_Y = TILE_Y + 2 * R; /* 40 x 24 */
-constexpr int PLANE_BYTES = WIN_X * WIN_Y * 4;                /* 3840 */
+#ifndef STENCIL25_TILE_Y
+#define STENCIL25_TILE_Y 32 /* 32 x 32 tile: 128 compute threads; 32 x 16 with twice the CTAs measured 6 % slower */
+#endif
+constexpr int TILE_X = 32, TILE_Y = STENCIL25_TILE_Y;
+constexpr int WIN_X = TILE_X + 2 * R, WIN_Y = TILE_Y + 2 * R; /* 40 x 40 */
+constexpr int PLANE_BYTES = WIN_X * WIN_Y * 4;                /* 6400 */
 constexpr int SLOTS = 2 * R + 1;                              /* 9 partial output planes */
 #ifndef STENCIL25_STAGES
 #define STENCIL25_STAGES 9 /* must divide SLOTS; nine keeps eight planes of loads in flight per CTA */
@@ -212,7 +215,7 @@ __device__ __forceinline__ void compute_side(RING &ring, const unsigned char *sm
   }
 }
 
-/* in_map: 3-D tensor map over the nx x ny x nz input (x fastest), box 40 x 24 x 1.
+/* in_map: 3-D tensor map over the nx x ny x nz input (x fastest), box 40 x 40 x 1.
  * Output planes [z_begin, z_end) are produced, blockIdx.z taking z_chunk of them;
  * input planes outside [0, nz) read as zero. Planes are numbered kp = 0 .. depth + 7
  * from (first output plane - 4); output plane kp - 8 is stored at step kp.
@@ -221,7 +224,7 @@ __device__ __forceinline__ void compute_side(RING &ring, const unsigned char *sm
  * The sharded driver points them into the z-neighbour GPUs' ghost planes (plain stores over
  * NVLink), shifted so that this rank's plane numbers land on the neighbour's. */
 #ifndef STENCIL25_MIN_BLOCKS
-#define STENCIL25_MIN_BLOCKS 4 /* four CTAs per SM need at most 170 registers; a fifth would spill */
+#define STENCIL25_MIN_BLOCKS 2 /* two CTAs of 160 threads per SM: eight compute warps, 167 registers */
 #endif
 __global__ void __launch_bounds__(COMPUTE_THREADS + DMA_THREADS, STENCIL25_MIN_BLOCKS)
 tensor_kernel(const __grid_constant__ CUtensorMap in_map, float *__restrict__ out, const Peers peer,
