@@ -35,7 +35,10 @@ constexpr int R = 4;
 #ifndef STENCIL25_TILE_Y
 #define STENCIL25_TILE_Y 32 /* 32 x 32 tile: 128 compute threads; 32 x 16 with twice the CTAs measured 6 % slower */
 #endif
-constexpr int TILE_X = 32, TILE_Y = STENCIL25_TILE_Y;
+#ifndef STENCIL25_TILE_X
+#define STENCIL25_TILE_X 32 /* 64 x 16 measured within 3 % of 32 x 32, 64 x 32 (one CTA per SM) slower */
+#endif
+constexpr int TILE_X = STENCIL25_TILE_X, TILE_Y = STENCIL25_TILE_Y;
 constexpr int WIN_X = TILE_X + 2 * R, WIN_Y = TILE_Y + 2 * R; /* 40 x 40 */
 constexpr int PLANE_BYTES = WIN_X * WIN_Y * 4;                /* 6400 */
 constexpr int SLOTS = 2 * R + 1;                              /* 9 partial output planes */
@@ -158,7 +161,7 @@ __device__ __forceinline__ void compute_side(RING &ring, const unsigned char *sm
                                              const Peers &peer, const int nx, const int ny, const int x0,
                                              const int y0, const int z0, const int depth, const Coeffs &k) {
   const int nplanes = depth + 2 * R;
-  const int tx = threadIdx.x & 7, ty = threadIdx.x >> 3;
+  const int tx = threadIdx.x % (TILE_X / 4), ty = threadIdx.x / (TILE_X / 4);
   const long long py = nx, pz = (long long)nx * ny;
   const long long cell0 = (long long)z0 * pz + (long long)(y0 + PY * ty) * py + x0 + 4 * tx;
   float *o = out + cell0;
