@@ -170,10 +170,33 @@ def median_launch_ms(fn, reps, flush=None):
     return ts[len(ts) // 2], ts[0]
 
 
-def seeded_field(n, seed):
-    g = torch.Generator(device="cuda")
-    g.manual_seed(seed)
-    return torch.rand(n, generator=g, device="cuda", dtype=torch.float32)
+def seeded_field(n, seed, lo=0.0, hi=1.0, first_index=0):
+    """Element i = lo + (hi - lo) * u(seed + first_index + i), the stateless splitmix64 rule that
+    oracle/oracle.c states for the benchmark inputs, made on the device (cudadma_fill_uniform)."""
+    import cudadma_b200 as cd
+    return cd.fill_uniform(torch.empty(n, device="cuda", dtype=torch.float32), seed, lo, hi, first_index)
+
+
+class SmClockProbe:
+    """The SM clock a workload really runs at: one-thread kernels on a second, high-priority
+    stream spin for a millisecond each beside it and report cycles / nanoseconds."""
+
+    def __init__(self, slots=64):
+        self.buf = torch.zeros(2 * slots, dtype=torch.int64, device="cuda")
+        self.stream = torch.cuda.Stream(priority=-1)
+        self.used, self.slots = 0, slots
+
+    def fire(self, spin_ns=1000000):
+        import cudadma_b200 as cd
+        if self.used < self.slots:
+            cd.clock_probe(self.buf[2 * self.used:], spin_ns, self.stream)
+            self.used += 1
+
+    def mhz(self):
+        torch.cuda.synchronize()
+        h = self.buf.cpu().view(-1, 2)[:self.used]
+        v = sorted(float(c) / float(ns) * 1e3 for c, ns in h.tolist() if ns > 0)
+        return v
 
 
 # ------------------------------------------------------------------ CPU baseline
@@ -224,9 +247,42 @@ def cpu_baseline_patterns():
 
 
 # ------------------------------------------------------------------ single-GPU patterns
+_EXPECTED = {}   # what the CPU oracle makes of the seeded inputs, computed once per process
+
+
+def expected(name):
+    """Inputs and expected outputs of the data-movement configurations from oracle/ (host side, the
+    checker): the same seeds as the device-side generator, so the kernels' results can be compared
+    bit for bit with what the reference's host check loops give."""
+    import numpy as np
+    from oracle import oracle
+    if name not in _EXPECTED:
+        if name == "sequential":
+            src = oracle.fill_uniform(1 << 24, 0xC1, -1.0, 1.0)
+            _EXPECTED[name] = oracle.chunked_copy(src)
+        elif name == "strided":
+            m = 16384
+            src = oracle.fill_uniform(m * m, 0xC2, -1.0, 1.0).reshape(m, m)
+            _EXPECTED[name] = oracle.tile_transpose(src)
+        elif name == "indirect":
+            n, rec = 1 << 22, 1 << 24
+            table = oracle.fill_uniform(rec * 8, 0xC3, -1.0, 1.0)
+            g, perm = oracle.fill_index(n, 0xC3A, rec), oracle.permutation(n, 0xC3B)
+            _EXPECTED[name] = (oracle.gather_scatter(np.zeros(n * 8, dtype=np.float32), table, g, perm), perm)
+    return _EXPECTED[name]
+
+
+def same_bits(dev_tensor, host_array):
+    import numpy as np
+    got = dev_tensor.cpu().numpy().reshape(-1).view(np.uint32)
+    return bool(np.array_equal(got, np.ascontiguousarray(host_array).reshape(-1).view(np.uint32)))
+
+
 def run_patterns(kind, peak):
     """Device-timed GB/s of the three data-movement patterns and the 512^3 stencil.
-    kind: "native", "portable" (this repository) or "reference" (oracle/_ref)."""
+    kind: "native", "portable" (this repository) or "reference" (oracle/_ref).
+    Inputs are the seeded fields of the benchmark list; every output of a timed launch is compared
+    bit for bit with the CPU oracle's."""
     import cudadma_b200 as cd
     if kind == "reference":
         from oracle import reference as ref
@@ -240,7 +296,7 @@ def run_patterns(kind, peak):
 
     # sequential: 64 MiB, 16 KiB chunks
     n = 1 << 24
-    src, dst = seeded_field(n, 0xC1) * 2 - 1, torch.empty(n, device="cuda")
+    src, dst = seeded_field(n, 0xC1, -1.0, 1.0), torch.zeros(n, device="cuda")
     if kind == "reference":
         f = lambda: ref.seq_copy(dst, src, n * 4)
     else:
@@ -249,10 +305,21 @@ def run_patterns(kind, peak):
         f()
     ms, best = median_launch_ms(f, 30, flush)
     res["sequential_64MiB"] = entry(ms, best, 2 * n * 4)
+    res["sequential_64MiB"]["parity"] = "pass" if same_bits(dst, expected("sequential")) else "FAIL"
+    # what a plain device-to-device copy of the same 64 MiB takes in the same loop (same L2 flush, same event
+    # pair): the job lasts under 30 us, most of which is the ramp of an idle GPU, whatever kernel runs
+    ceil_dst = torch.empty_like(dst)
+    g = lambda: ceil_dst.copy_(src)
+    for _ in range(3):
+        g()
+    msc, bestc = median_launch_ms(g, 30, flush)
+    res["sequential_64MiB"]["copy_ceiling_gbs"] = round(2 * n * 4 / msc / 1e6, 1)
+    res["sequential_64MiB"]["copy_ceiling_note"] = "torch copy_ (cudaMemcpyAsync device-to-device) of the same array, same loop"
+    del ceil_dst
     # The same 64 MiB job back to back over 12 different array pairs (1.5 GiB in all, so nothing is found
     # in L2 either): one event pair around 24 launches, which takes the event pair's own microseconds
     # (a tenth of such a short launch) out of the figure.
-    pairs = [(seeded_field(n, 0xC10 + i), torch.empty(n, device="cuda")) for i in range(12)]
+    pairs = [(seeded_field(n, 0xC10 + i, -1.0, 1.0), torch.empty(n, device="cuda")) for i in range(12)]
     cur_stream = torch.cuda.current_stream().cuda_stream  # looked up once: the launches must not wait for Python
     if kind == "reference":
         rot = lambda: [ref.seq_copy(d, s_, n * 4) for _ in range(2) for s_, d in pairs]
@@ -262,10 +329,14 @@ def run_patterns(kind, peak):
     msr, bestr = median_launch_ms(rot, 10)
     res["sequential_64MiB"]["rotating_gbs"] = round(2 * n * 4 * 2 * len(pairs) / msr / 1e6, 1)
     res["sequential_64MiB"]["rotating_frac_of_peak"] = round(2 * n * 4 * 2 * len(pairs) / msr / 1e6 / peak, 4)
+    rotc = lambda: [d.copy_(s_) for _ in range(2) for s_, d in pairs]
+    rotc()
+    msrc, _ = median_launch_ms(rotc, 10)
+    res["sequential_64MiB"]["rotating_copy_ceiling_gbs"] = round(2 * n * 4 * 2 * len(pairs) / msrc / 1e6, 1)
     del pairs
     # the same kernel on 1 GiB, where launch and tail effects no longer dominate
     nb = 1 << 28
-    big_s, big_d = seeded_field(nb, 0xC1), torch.empty(nb, device="cuda")
+    big_s, big_d = seeded_field(nb, 0xC1, -1.0, 1.0), torch.empty(nb, device="cuda")
     if kind == "reference":
         f = lambda: ref.seq_copy(big_d, big_s, nb * 4)
     else:
@@ -276,11 +347,16 @@ def run_patterns(kind, peak):
     res["sequential_1GiB"] = entry(ms, best, 2 * nb * 4)
     ok = torch.equal(big_d.view(torch.int32), big_s.view(torch.int32))
     res["sequential_1GiB"]["parity"] = "pass" if ok else "FAIL"
+    g = lambda: big_d.copy_(big_s)
+    for _ in range(3):
+        g()
+    msc, _ = median_launch_ms(g, 10)
+    res["sequential_1GiB"]["copy_ceiling_gbs"] = round(2 * nb * 4 / msc / 1e6, 1)
     del big_s, big_d, src, dst
 
     # strided: 16384 x 16384 transpose in 128 x 64 tiles (1 GiB in, 1 GiB out: larger than L2)
     m = 16384
-    a, b = seeded_field(m * m, 0xC2) * 2 - 1, torch.empty(m * m, device="cuda")
+    a, b = seeded_field(m * m, 0xC2, -1.0, 1.0), torch.zeros(m * m, device="cuda")
     if kind == "reference":
         f = lambda: ref.strided_transpose(b, a, m, m)
     else:
@@ -289,16 +365,15 @@ def run_patterns(kind, peak):
         f()
     ms, best = median_launch_ms(f, 10)
     res["strided_16384"] = entry(ms, best, 2 * m * m * 4)
-    res["strided_16384"]["parity"] = "pass" if torch.equal(b.view(m, m)[:512], a.view(m, m).t()[:512]) else "FAIL"
+    res["strided_16384"]["parity"] = "pass" if same_bits(b, expected("strided")) else "FAIL"
     del a, b
 
     # indirect: 2^24 x 32 B table, 2^22 gathers, scattered through a permutation
     n, rec = 1 << 22, 1 << 24
-    g = torch.Generator(device="cuda")
-    g.manual_seed(0xC3A)
-    table = seeded_field(rec * 8, 0xC3)
-    gi = torch.randint(0, rec, (n,), generator=g, device="cuda", dtype=torch.int32)
-    si = torch.randperm(n, generator=g, device="cuda").to(torch.int32)
+    want, perm = expected("indirect")
+    table = seeded_field(rec * 8, 0xC3, -1.0, 1.0)
+    gi = cd.fill_index(torch.empty(n, dtype=torch.int32, device="cuda"), 0xC3A, rec)
+    si = torch.from_numpy(perm).cuda()
     out = torch.zeros(n * 8, device="cuda")
     if kind == "reference":
         f = lambda: ref.gather_scatter(out, table, gi, si, n)
@@ -309,10 +384,8 @@ def run_patterns(kind, peak):
     ms, best = median_launch_ms(f, 20, flush)
     res["indirect_2e22x32B"] = entry(ms, best, n * 72)
     res["indirect_2e22x32B"]["payload_gbs"] = round(n * 64 / ms / 1e6, 1)
-    exp = torch.empty(n, 8, device="cuda")
-    exp[si.long()] = table.view(rec, 8)[gi.long()]
-    res["indirect_2e22x32B"]["parity"] = "pass" if torch.equal(out.view(n, 8), exp) else "FAIL"
-    del out, exp
+    res["indirect_2e22x32B"]["parity"] = "pass" if same_bits(out, want) else "FAIL"
+    del out
     if kind != "reference":
         # The same 512 MiB table read as 2^22 records of 128 bytes: every record is one whole DRAM
         # line, so this is what random line fetches sustain; a 32-byte record costs such a line too.
@@ -397,6 +470,69 @@ def make_stencil(impl, nz_global, weights=None):
     return ShardedStencil(NX, NY, nz_global, step_fn=step, pad_xy=4, device=torch.device("cuda", torch.cuda.current_device()))
 
 
+def slab_of_global_field(st):
+    """This rank's planes of the one global seeded field (seed 0xC4, uniform [0, 1))."""
+    return seeded_field(NX * NY * st.nzl, 0xC4, 0.0, 1.0, first_index=st.z_lo * NX * NY)
+
+
+def sharded_parity(st, world, steps=3):
+    """Correctness of the sharded step inside the measured run. The object is reloaded with its
+    planes of the global seeded field and stepped `steps` times with halo exchange; every rank then
+    recomputes its own planes ALONE, by plain single-GPU steps on the planes [z_lo - 4 steps,
+    z_hi + 4 steps) of the same global field (cut at the grid's ends), where nothing depends on a
+    neighbour: whatever the cut does wrong travels four planes per step and has not reached the
+    owned planes. The two must agree bit for bit on every rank. On one GPU, where there is nothing to
+    exchange, the first planes of the result are compared with the double-precision CPU oracle."""
+    import cudadma_b200 as cd
+    nz = st.nz
+    torch.cuda.synchronize()
+    barrier()  # no neighbour still pushes planes of the timed steps while this rank reloads its arrays
+    st.load(slab_of_global_field(st))
+    got = st.run(steps)
+    lo, hi = max(0, st.z_lo - 4 * steps), min(nz, st.z_hi + 4 * steps)
+    if world > 1:
+        pts = NX * NY * (hi - lo)
+        a = seeded_field(pts, 0xC4, 0.0, 1.0, first_index=lo * NX * NY)
+        b = torch.zeros_like(a)
+        alone = cd.stencil25_run(a, b, NX, NY, hi - lo, steps).view(hi - lo, NY, NX)[st.z_lo - lo:st.z_hi - lo]
+        ok = bool(torch.equal(alone.view(torch.int32), got.contiguous().view(torch.int32)))
+        t = torch.tensor([1 if ok else 0], dtype=torch.int32, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        verdict = "pass" if int(t.item()) == 1 else "FAIL"
+        del a, b, alone
+        return {"parity": verdict, "how": "%d steps with halo exchange on every rank against the same planes stepped alone on "
+                                          "that rank from the global seeded field: bit-identical on all %d ranks" % (steps, world)
+                if verdict == "pass" else "a rank's sharded planes differ from its planes stepped alone"}
+    import numpy as np
+    from oracle import oracle
+    planes = 24
+    field = oracle.fill_uniform(NX * NY * (planes + 4 * steps), 0xC4, 0.0, 1.0).reshape(planes + 4 * steps, NY, NX)
+    exp = oracle.stencil25_f64(field, cd.STENCIL_COEFFS, steps)[:planes]
+    res = got[:planes].cpu().numpy()
+    err = float(np.abs(res.astype(np.float64) - exp).max() / np.abs(exp).max())
+    return {"parity": "pass" if err <= 1e-5 else "FAIL", "rel_err": err,
+            "how": "%d steps of the whole grid from the global seeded field; the first %d planes against the double-precision "
+                   "CPU oracle (max |gpu - ref| / max |ref| <= 1e-5)" % (steps, planes)}
+
+
+def copy_rate_now(seconds):
+    """GB/s of a plain device copy (torch copy_ of 1 GiB, read + write bytes) sustained for about
+    `seconds`, right now: the copy bandwidth of the GPU in the power state the measured region left it in."""
+    n = 1 << 28
+    a, b = torch.empty(n, device="cuda"), torch.empty(n, device="cuda")
+    a.zero_()
+    b.copy_(a)
+    torch.cuda.synchronize()
+    reps = max(4, int(seconds * 6.0e12 / (8.0 * n)))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        b.copy_(a)
+    e1.record()
+    torch.cuda.synchronize()
+    return 8.0 * n * reps / e0.elapsed_time(e1) / 1e6
+
+
 def run_stencil_job(impl, args, rank, world, local, peak, peak_kind):
     import cudadma_b200 as cd
     rates = None
@@ -405,18 +541,22 @@ def run_stencil_job(impl, args, rank, world, local, peak, peak_kind):
     st = make_stencil(impl, NZ, rates)
     planes = [st.nzl]
     if world > 1:
-        import torch.distributed as dist
         planes = [None] * world
         dist.all_gather_object(planes, st.nzl)
     slab_pts = NX * NY * st.nzl
-    st.load(seeded_field(slab_pts, 0xC4 + rank))
+    st.load(slab_of_global_field(st))
     for _ in range(max(args.warmup, 3)):
         st.step()
+    probe = SmClockProbe()
     with ClockSampler(local) as clocks:
+        probe.fire()
         ms = time_region(st.step, args.steps)
+        copy_gbs = copy_rate_now(ms / 1e3)
         if ms < 400.0:  # give the sampler a few periods: repeat the same region, untimed for the record
             reps = int(400.0 / max(ms, 1e-3))
-            for _ in range(reps):
+            for i in range(reps):
+                if i % 4 == 0:
+                    probe.fire()
                 for _ in range(args.steps):
                     st.step()
             torch.cuda.synchronize()
@@ -424,6 +564,8 @@ def run_stencil_job(impl, args, rank, world, local, peak, peak_kind):
     value = pts * args.steps / ms / 1e6  # Gpts/s, whole job
     per_step_ms = ms / args.steps
     status = cd.device_status() if impl == "ours" else 0
+    sm_mhz = probe.mhz()
+    parity = sharded_parity(st, world) if impl == "ours" else None
 
     # weak-scaling companion: 256 planes per GPU (the 8-GPU point is the configuration above)
     weak = None
@@ -431,12 +573,19 @@ def run_stencil_job(impl, args, rank, world, local, peak, peak_kind):
         del st
         torch.cuda.empty_cache()
         stw = make_stencil(impl, 256 * world, rates)
-        stw.load(seeded_field(NX * NY * stw.nzl, 0xC4 + rank))
+        stw.load(seeded_field(NX * NY * stw.nzl, 0xC4, 0.0, 1.0, first_index=stw.z_lo * NX * NY))
         for _ in range(3):
             stw.step()
         msw = time_region(stw.step, args.steps)
         weak = {"grid": [NX, NY, 256 * world], "value": round(NX * NY * 256 * world * args.steps / msw / 1e6, 2),
                 "unit": "Gpts/s", "ms_per_step": round(msw / args.steps, 4)}
+        # the same object a while later, when the GPUs have settled at their power cap (the figure
+        # above is the first 20 steps after a pause)
+        for _ in range(30):
+            for _ in range(args.steps):
+                stw.step()
+        msw2 = time_region(stw.step, args.steps)
+        weak["settled_ms_per_step"] = round(msw2 / args.steps, 4)
         del stw
         torch.cuda.empty_cache()
         st = make_stencil(impl, NZ, rates)
@@ -444,7 +593,7 @@ def run_stencil_job(impl, args, rank, world, local, peak, peak_kind):
     # end to end: pinned host slab -> device, K steps with halo exchange, device -> pinned host slab
     h_in = torch.empty(slab_pts, dtype=torch.float32).pin_memory()
     h_out = torch.empty(slab_pts, dtype=torch.float32).pin_memory()
-    h_in.uniform_(0.0, 1.0)
+    h_in.copy_(slab_of_global_field(st))
     st.run_host(h_out, h_in, 1)  # warm-up (also faults the pinned pages in)
     torch.cuda.synchronize()
     barrier()
@@ -478,6 +627,13 @@ def run_stencil_job(impl, args, rank, world, local, peak, peak_kind):
         e2e["parity"] = "pass (bit-identical to the device-resident run)" if same else "FAIL"
     del h_in, h_out
 
+    clock_rec = clocks.summary()
+    if sm_mhz:
+        clock_rec["sm_mhz_in_kernel"] = {"first": round(probe_first(probe), 0), "median": round(sm_mhz[len(sm_mhz) // 2], 0),
+                                         "min": round(sm_mhz[0], 0),
+                                         "how": "one-thread probe kernels beside the steps: SM cycles / nanoseconds; `first` ran "
+                                                "inside the timed region, the others during the repeats of it"}
+    achieved = BYTES_PER_POINT * pts / world / per_step_ms / 1e6
     line = {
         "metric": "stencil Gpts/s (radius-4 25-point fp32, %dx%dx%d z-sharded over N GPUs)" % (NX, NY, NZ),
         "value": round(value, 2), "unit": "Gpts/s", "n_gpus": world, "steps": args.steps,
@@ -489,21 +645,34 @@ def run_stencil_job(impl, args, rank, world, local, peak, peak_kind):
                    "slab_balance": ({"rates_gpts": rates, "note": "slabs cut in proportion to each GPU's stencil rate, "
                                      "measured alone on a 256-plane field just before"} if rates else "equal slabs"),
                    "exchange": ("none" if world == 1 else "torch.distributed send/recv (NCCL)" if (impl != "ours" or EXCHANGE == "nccl")
-                                else "boundary kernel stores into the neighbours' ghost planes over NVLink (CUDA IPC), flag handshake"),
+                                else "one launch per step: boundary CTAs wait for the neighbours' step count, store their planes into "
+                                     "the neighbours' ghost planes over NVLink (CUDA IPC) and publish this rank's count"),
                    "l2": "inputs larger than L2 (%.1f GiB per array per GPU)" % (slab_pts * 4 / 2**30),
-                   "synthetic_for": "uniform[0,1) field from a seeded generator"},
-        "roofline": {"bound": "hbm", "achieved": round(BYTES_PER_POINT * pts / world / per_step_ms / 1e6, 1),
+                   "synthetic_for": "uniform[0,1) field, element i = u(splitmix64(0xC4 + i)), the same global field at every N"},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1),
                      "peak": peak, "unit": "GB/s",
-                     "frac": round(BYTES_PER_POINT * pts / world / per_step_ms / 1e6 / peak, 4),
+                     "frac": round(achieved / peak, 4),
                      "traffic": int(STENCIL_DRAM_BYTES_PER_POINT * pts / world) if impl == "ours" else None,
                      "peak_kind": "of " + peak_kind,
                      "kernel": "stencil25::tensor_kernel" if impl == "ours" else "portable::stencil_kernel",
-                     "algorithmic_bytes_per_launch": BYTES_PER_POINT * pts // world},
-        "e2e": e2e, "clocks": clocks.summary(), "device_status": status,
+                     "algorithmic_bytes_per_launch": BYTES_PER_POINT * pts // world,
+                     "copy_gbs_right_after": round(copy_gbs, 1),
+                     "frac_of_copy_right_after": round(achieved / copy_gbs, 4),
+                     "copy_note": "a plain device copy (torch copy_, 1 GiB, read + write bytes) run for as long as the timed "
+                                  "region, directly after it, on rank 0's GPU: the copy bandwidth in the same power state"},
+        "e2e": e2e, "clocks": clock_rec, "device_status": status,
     }
+    if parity is not None:
+        line["parity"] = parity["parity"]
+        line["parity_detail"] = parity
     if weak is not None:
         line["weak"] = weak
     return line, st
+
+
+def probe_first(probe):
+    h = probe.buf.cpu().view(-1, 2)[0].tolist()
+    return float(h[0]) / float(h[1]) * 1e3 if h[1] else 0.0
 
 
 def profile_case(case, reps):
@@ -527,26 +696,19 @@ def profile_case(case, reps):
         a, b = seeded_field(m * m, 0xC2), torch.empty(m * m, device="cuda")
         for _ in range(reps):
             cd.strided_transpose(b, a, m, m)
-    elif case == "indirect":
+    elif case in ("indirect", "indirect_tma", "indirect_scatter4", "indirect_portable"):
         n, rec = 1 << 22, 1 << 24
-        g = torch.Generator(device="cuda")
-        g.manual_seed(0xC3A)
-        table = seeded_field(rec * 8, 0xC3)
-        gi = torch.randint(0, rec, (n,), generator=g, device="cuda", dtype=torch.int32)
-        si = torch.randperm(n, generator=g, device="cuda").to(torch.int32)
+        table = seeded_field(rec * 8, 0xC3, -1.0, 1.0)
+        gi = cd.fill_index(torch.empty(n, dtype=torch.int32, device="cuda"), 0xC3A, rec)
+        si = torch.randperm(n, device="cuda").to(torch.int32)
         out = torch.zeros(n * 8, device="cuda")
         for _ in range(reps):
-            cd.gather_scatter(out, table, gi, si, n)
-    elif case == "indirect_tma":
-        n, rec = 1 << 22, 1 << 24
-        g = torch.Generator(device="cuda")
-        g.manual_seed(0xC3A)
-        table = seeded_field(rec * 8, 0xC3)
-        gi = torch.randint(0, rec, (n,), generator=g, device="cuda", dtype=torch.int32)
-        si = torch.randperm(n, generator=g, device="cuda").to(torch.int32)
-        out = torch.zeros(n * 8, device="cuda")
-        for _ in range(reps):
-            cd.gather_scatter_tma(out, table, rec, gi, si, n)
+            if case == "indirect":
+                cd.gather_scatter(out, table, gi, si, n)
+            elif case == "indirect_portable":
+                cd.gather_scatter(out, table, gi, si, n, 32, "portable")
+            else:
+                cd.gather_scatter_tma(out, n, table, rec, gi, si, n, 32, 1 if case == "indirect_tma" else 2)
     else:
         raise SystemExit("unknown case " + case)
     torch.cuda.synchronize()
@@ -579,7 +741,8 @@ def main():
     ap.add_argument("--exchange", default="p2p", choices=("p2p", "nccl"),
                     help="halo exchange at N > 1: peer-to-peer stores from the boundary kernel, or NCCL send/recv")
     ap.add_argument("--profile-case", default=None,
-                    help="run only a small case of one kernel (stencil_512, sequential, strided, indirect, indirect_tma) "
+                    help="run only a small case of one kernel (stencil_512, sequential, strided, indirect, indirect_tma, "
+                         "indirect_scatter4, indirect_portable) "
                          "--steps times, for a profiler capture")
     args = ap.parse_args()
     global EXCHANGE
@@ -624,12 +787,12 @@ def main():
     del st
     torch.cuda.empty_cache()
     if impl == "ours":
-        # launches of this library per timed step: one kernel at N = 1, three (two boundary runs + interior) at N > 1
-        # p2p: wait kernel, stencil kernel, signal kernel; nccl: two boundary launches and the interior launch
+        # launches of this library per timed step: one kernel (p2p folds the neighbour handshake into it);
+        # the nccl form makes three (two boundary runs and the interior)
         if world > 1:
             line["config"]["host_threads"] = ("each rank bound to the %d cores NVML lists for its GPU" % len(HOST_CORES)) if HOST_CORES \
                 else "not bound (no NVML core list)"
-        line["gpu_launches"] = args.steps * (1 if world == 1 else 3)
+        line["gpu_launches"] = args.steps * (1 if (world == 1 or EXCHANGE == "p2p") else 3)
         line["launches_total_this_process"] = cd.launch_count() - before
     else:
         line["impl"] = "reference"

@@ -31,7 +31,18 @@ SYMBOLS = [
     ("cudadma_gather_scatter", _c.c_int,
      [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_int, _c.c_int, _c.c_void_p]),
     ("cudadma_gather_scatter_tma", _c.c_int,
-     [_c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_int, _c.c_void_p]),
+     [_c.c_void_p, _c.c_size_t, _c.c_void_p, _c.c_size_t, _c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_int, _c.c_int,
+      _c.c_void_p]),
+    ("cudadma_make_tensor_map_2d", _c.c_int,
+     [_c.c_void_p, _c.c_void_p, _c.c_ulonglong, _c.c_ulonglong, _c.c_ulonglong, _c.c_uint, _c.c_uint, _c.c_int]),
+    ("cudadma_make_tensor_map_3d", _c.c_int,
+     [_c.c_void_p, _c.c_void_p, _c.c_ulonglong, _c.c_ulonglong, _c.c_ulonglong, _c.c_ulonglong, _c.c_ulonglong,
+      _c.c_uint, _c.c_uint, _c.c_uint]),
+    ("cudadma_fill_uniform", _c.c_int,
+     [_c.c_void_p, _c.c_size_t, _c.c_ulonglong, _c.c_ulonglong, _c.c_float, _c.c_float, _c.c_void_p]),
+    ("cudadma_fill_index", _c.c_int,
+     [_c.c_void_p, _c.c_size_t, _c.c_ulonglong, _c.c_ulonglong, _c.c_uint, _c.c_void_p]),
+    ("cudadma_clock_probe", _c.c_int, [_c.c_void_p, _c.c_longlong, _c.c_void_p]),
     ("cudadma_stencil25_step", _c.c_int,
      [_c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.POINTER(_c.c_float), _c.c_int,
       _c.c_int, _c.c_void_p]),
@@ -47,9 +58,20 @@ SYMBOLS = [
     ("cudadma_slab_handle_bytes", _c.c_size_t, []),
     ("cudadma_slab_export", _c.c_int, [_c.c_void_p, _c.c_void_p]),
     ("cudadma_slab_connect", _c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p]),
+    ("cudadma_slab_connect_local", _c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p]),
+    ("cudadma_slab_set_wait_limit", _c.c_int, [_c.c_void_p, _c.c_longlong]),
     ("cudadma_slab_buffer", _c.c_int, [_c.c_void_p, _c.c_int, _c.POINTER(_c.c_void_p)]),
     ("cudadma_slab_step", _c.c_int, [_c.c_void_p, _c.POINTER(_c.c_float), _c.c_void_p]),
+    ("cudadma_slab_status", _c.c_int, [_c.c_void_p, _c.c_void_p]),
     ("cudadma_slab_destroy", _c.c_int, [_c.c_void_p]),
+    ("cudadma_stencil25_multi_create", _c.c_int,
+     [_c.POINTER(_c.c_void_p), _c.c_int, _c.POINTER(_c.c_int), _c.c_int, _c.c_int, _c.c_int]),
+    ("cudadma_stencil25_multi_load", _c.c_int, [_c.c_void_p, _c.c_void_p]),
+    ("cudadma_stencil25_multi_run", _c.c_int, [_c.c_void_p, _c.POINTER(_c.c_float), _c.c_int]),
+    ("cudadma_stencil25_multi_store", _c.c_int, [_c.c_void_p, _c.c_void_p]),
+    ("cudadma_stencil25_multi_slab", _c.c_int,
+     [_c.c_void_p, _c.c_int, _c.POINTER(_c.c_void_p), _c.POINTER(_c.c_int), _c.POINTER(_c.c_int)]),
+    ("cudadma_stencil25_multi_destroy", _c.c_int, [_c.c_void_p]),
     ("cudadma_seq_copy_host", _c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_int, _c.c_int]),
     ("cudadma_strided_transpose_host", _c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int]),
     ("cudadma_gather_scatter_host", _c.c_int,
@@ -173,14 +195,56 @@ def gather_scatter(out, table, gather_idx, scatter_idx, n=None, record_bytes=32,
                                         _IMPLS[impl], _stream(stream)))
 
 
-def gather_scatter_tma(out, table, table_records, gather_idx, scatter_idx, n=None, record_bytes=32, stream=None):
-    """gather_scatter with the gather issued as TMA row gathers (four records per instruction)."""
+def gather_scatter_tma(out, out_records, table, table_records, gather_idx, scatter_idx, n=None, record_bytes=32,
+                       mode=1, stream=None):
+    """gather_scatter with TMA row instructions, four records each: mode 1 = gather4 loads,
+    2 = scatter4 stores, 3 = both."""
     _require_cuda(out, table, gather_idx, scatter_idx)
     if n is None:
         n = gather_idx.numel()
     _check("cudadma_gather_scatter_tma",
-           lib().cudadma_gather_scatter_tma(_ptr(out), _ptr(table), table_records, _ptr(gather_idx),
-                                            _ptr(scatter_idx), n, record_bytes, _stream(stream)))
+           lib().cudadma_gather_scatter_tma(_ptr(out), out_records, _ptr(table), table_records, _ptr(gather_idx),
+                                            _ptr(scatter_idx), n, record_bytes, mode, _stream(stream)))
+
+
+def make_tensor_map_2d(base, cols, rows, row_pitch_bytes, box_cols, box_rows, swizzle_128b=False):
+    """A 128-byte CUtensorMap (as a ctypes buffer, 64-byte aligned) over a 2-D array of 4-byte words."""
+    raw = ctypes.create_string_buffer(128 + 64)
+    addr = (ctypes.addressof(raw) + 63) & ~63
+    _check("cudadma_make_tensor_map_2d",
+           lib().cudadma_make_tensor_map_2d(addr, _ptr(base), cols, rows, row_pitch_bytes, box_cols, box_rows,
+                                            int(bool(swizzle_128b))))
+    return ctypes.string_at(addr, 128)
+
+
+def make_tensor_map_3d(base, nx, ny, nz, row_pitch_bytes, plane_pitch_bytes, box_x, box_y, box_z):
+    raw = ctypes.create_string_buffer(128 + 64)
+    addr = (ctypes.addressof(raw) + 63) & ~63
+    _check("cudadma_make_tensor_map_3d",
+           lib().cudadma_make_tensor_map_3d(addr, _ptr(base), nx, ny, nz, row_pitch_bytes, plane_pitch_bytes, box_x,
+                                            box_y, box_z))
+    return ctypes.string_at(addr, 128)
+
+
+def fill_uniform(dst, seed, lo=0.0, hi=1.0, first_index=0, n=None, stream=None):
+    """dst[i] = lo + (hi - lo) * u(seed + first_index + i): the seeded generator of the benchmark inputs."""
+    _require_cuda(dst)
+    n = dst.numel() if n is None else n
+    _check("cudadma_fill_uniform", lib().cudadma_fill_uniform(_ptr(dst), n, seed, first_index, lo, hi, _stream(stream)))
+    return dst
+
+
+def fill_index(dst, seed, modulo, first_index=0, n=None, stream=None):
+    _require_cuda(dst)
+    n = dst.numel() if n is None else n
+    _check("cudadma_fill_index", lib().cudadma_fill_index(_ptr(dst), n, seed, first_index, modulo, _stream(stream)))
+    return dst
+
+
+def clock_probe(out, spin_ns, stream=None):
+    """out: int64 CUDA tensor of two elements; receives SM cycles and nanoseconds of a spin_ns spin."""
+    _require_cuda(out)
+    _check("cudadma_clock_probe", lib().cudadma_clock_probe(_ptr(out), spin_ns, _stream(stream)))
 
 
 def stencil25_step(out, inp, nx, ny, nz, z_begin=0, z_end=None, coeff=None, z_chunk=0, impl="native", stream=None):
@@ -244,6 +308,19 @@ class Slab:
     def connect(self, lower, upper):
         _check("cudadma_slab_connect", lib().cudadma_slab_connect(self._h, lower, upper))
 
+    def connect_local(self, lower, upper):
+        """Joins slabs of this process: lower / upper are Slab objects (or None)."""
+        _check("cudadma_slab_connect_local",
+               lib().cudadma_slab_connect_local(self._h, lower._h if lower is not None else None,
+                                                upper._h if upper is not None else None))
+
+    def set_wait_limit(self, sm_cycles):
+        _check("cudadma_slab_set_wait_limit", lib().cudadma_slab_set_wait_limit(self._h, int(sm_cycles)))
+
+    def status(self, stream=None):
+        """Synchronises the stream; OK, or ERR_TIMEOUT once a wait for a neighbour has given up."""
+        return lib().cudadma_slab_status(self._h, _stream(stream))
+
     def buffer_address(self, which=0):
         p = ctypes.c_void_p()
         _check("cudadma_slab_buffer", lib().cudadma_slab_buffer(self._h, which, ctypes.byref(p)))
@@ -265,6 +342,45 @@ class Slab:
     def destroy(self):
         if self._h is not None:
             lib().cudadma_slab_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass
+
+
+class MultiStencil:
+    """The sharded stencil driven from this one process through cudadma_stencil25_multi_*: one slab
+    per entry of `devices` (default: GPUs 0 .. n_gpus - 1; repeated entries put several slabs on
+    one GPU), host fields in, host fields out."""
+
+    def __init__(self, n_gpus, nx, ny, nz, devices=None):
+        self.n, self.nx, self.ny, self.nz = n_gpus, nx, ny, nz
+        h = ctypes.c_void_p()
+        dev = None if devices is None else (ctypes.c_int * n_gpus)(*[int(d) for d in devices])
+        _check("cudadma_stencil25_multi_create", lib().cudadma_stencil25_multi_create(ctypes.byref(h), n_gpus, dev, nx, ny, nz))
+        self._h = h
+
+    def load(self, h_field):
+        _check("cudadma_stencil25_multi_load", lib().cudadma_stencil25_multi_load(self._h, _ptr(h_field)))
+
+    def run(self, steps, coeff=None):
+        _check("cudadma_stencil25_multi_run", lib().cudadma_stencil25_multi_run(self._h, _coeffs(coeff), steps))
+
+    def store(self, h_field):
+        _check("cudadma_stencil25_multi_store", lib().cudadma_stencil25_multi_store(self._h, _ptr(h_field)))
+
+    def planes(self, rank):
+        lo, hi = ctypes.c_int(), ctypes.c_int()
+        _check("cudadma_stencil25_multi_slab",
+               lib().cudadma_stencil25_multi_slab(self._h, rank, None, ctypes.byref(lo), ctypes.byref(hi)))
+        return lo.value, hi.value
+
+    def destroy(self):
+        if self._h is not None:
+            lib().cudadma_stencil25_multi_destroy(self._h)
             self._h = None
 
     def __del__(self):

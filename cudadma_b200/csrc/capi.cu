@@ -78,12 +78,29 @@ int launched() {
   return CUDADMA_OK;
 }
 
+/* What the library remembers per device (a process may drive several): values are looked up on
+ * first use with that device current. Races between threads only repeat a lookup. */
+constexpr int MAX_DEVICES = 64;
+struct DeviceState {
+  std::atomic<int> sms{0};
+  std::atomic<bool> stencil_smem{false};   /* tensor_kernel may use its dynamic shared memory */
+  std::atomic<int> gather_fit[4] = {{0}, {0}, {0}, {0}}; /* resident CTAs per SM of gather_scatter_kernel, by record size */
+};
+DeviceState g_dev[MAX_DEVICES];
+
+int current_device() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return -1;
+  return dev;
+}
+
 int sm_count() {
-  static int n = 0;
+  const int dev = current_device();
+  if (dev < 0) return 0;
+  int n = g_dev[dev].sms.load();
   if (n == 0) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) n = 0;
+    g_dev[dev].sms.store(n);
   }
   return n;
 }
@@ -187,45 +204,106 @@ int finish_status(cudaStream_t s) {
   return w ? CUDADMA_ERR_TIMEOUT : CUDADMA_OK;
 }
 
+/* The last few stencil tensor maps of the calling thread, by what they were encoded from: a time
+ * loop alternates between two arrays, so it encodes twice and then only looks up. */
+struct MapKey { const void *base; int nx, ny, nz; };
+struct MapSlot { MapKey key; CUtensorMap map; };
+thread_local MapSlot t_maps[4];
+thread_local int t_maps_next = 0;
+
+int stencil_map(const CUtensorMap **out, const float *in, int nx, int ny, int nz) {
+  for (int i = 0; i < 4; ++i) {
+    const MapKey &k = t_maps[i].key;
+    if (k.base == in && k.nx == nx && k.ny == ny && k.nz == nz) { *out = &t_maps[i].map; return CUDADMA_OK; }
+  }
+  MapSlot &slot = t_maps[t_maps_next];
+  t_maps_next = (t_maps_next + 1) & 3;
+  slot.key = MapKey{nullptr, 0, 0, 0};
+  const cuuint64_t dims[3] = {(cuuint64_t)nx, (cuuint64_t)ny, (cuuint64_t)nz};
+  const cuuint64_t strides[2] = {(cuuint64_t)nx * 4, (cuuint64_t)nx * ny * 4};
+  const cuuint32_t box[3] = {stencil25::WIN_X, stencil25::WIN_Y, 1};
+  if (int r = make_map_f32(&slot.map, in, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, STENCIL25_L2PROMO)) return r;
+  slot.key = MapKey{in, nx, ny, nz};
+  *out = &slot.map;
+  return CUDADMA_OK;
+}
+
+/* How the output planes of a launch are cut into runs, one run per CTA and tile (see tensor_kernel). */
+struct ChunkPlan { int z_chunk, z_edge, zc; };
+
+ChunkPlan plan_chunks(int depth, long long tiles, int sms, int z_chunk, int z_edge) {
+  ChunkPlan p;
+  if (z_edge > 0 && depth < 2 * z_edge + 1) z_edge = 0;
+  const int inner = depth - 2 * z_edge;
+  if (z_chunk <= 0) {
+    /* enough CTAs for a few waves over the SMs, but runs of at least 32 planes so that the
+     * eight lead-in/lead-out planes of a run stay a small share of its loads */
+    const long long want = (long long)STENCIL_CTAS_TARGET * sms - (z_edge > 0 ? 2 * tiles : 0);
+    long long chunks = (want + tiles - 1) / tiles;
+    if (chunks < 1) chunks = 1;
+    z_chunk = (int)((inner + chunks - 1) / chunks);
+    if (z_chunk < 32) z_chunk = 32;
+  }
+  if (z_chunk > inner) z_chunk = inner;
+  p.z_chunk = z_chunk;
+  p.z_edge = z_edge;
+  p.zc = (inner + z_chunk - 1) / z_chunk + (z_edge > 0 ? 2 : 0);
+  return p;
+}
+
+/* CTAs of a launch whose run of planes reaches into a pushed range (same rule as the kernel's) */
+unsigned int boundary_ctas(const ChunkPlan &p, long long tiles, const stencil25::Peers &peer, int z_begin, int z_end) {
+  long long n = 0;
+  for (int bz = 0; bz < p.zc; ++bz) {
+    int z0, depth;
+    if (p.z_edge > 0) {
+      if (bz == 0) { z0 = z_begin; depth = p.z_edge; }
+      else if (bz == 1) { z0 = z_end - p.z_edge; depth = p.z_edge; }
+      else {
+        z0 = z_begin + p.z_edge + (bz - 2) * p.z_chunk;
+        depth = (z_end - p.z_edge - z0 < p.z_chunk) ? (z_end - p.z_edge - z0) : p.z_chunk;
+      }
+    } else {
+      z0 = z_begin + bz * p.z_chunk;
+      depth = (z_end - z0 < p.z_chunk) ? (z_end - z0) : p.z_chunk;
+    }
+    if ((peer.lo && z0 < peer.lo_end) || (peer.hi && z0 + depth > peer.hi_begin)) n += tiles;
+  }
+  return (unsigned int)n;
+}
+
+const stencil25::Sync NO_SYNC = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0u, 0u, 0};
+
 /* Launch of the tensor-map stencil kernel on output planes [z_begin, z_end); `peer` names second
- * destinations for the lowest and highest planes (see stencil25::Peers). */
-int launch_stencil_native(float *out, const stencil25::Peers &peer, const float *in, int nx, int ny, int nz, int z_begin, int z_end,
-                          const float coeff[5], int z_chunk, cudaStream_t s) {
+ * destinations for the lowest and highest planes (see stencil25::Peers), `sync` the handshake with
+ * the neighbour ranks (its boundary_ctas is filled in here), z_edge the depth of the two boundary
+ * runs (0: equal runs). */
+int launch_stencil_native(float *out, const stencil25::Peers &peer, stencil25::Sync sync, const float *in, int nx, int ny,
+                          int nz, int z_begin, int z_end, const float coeff[5], int z_chunk, int z_edge, cudaStream_t s) {
   const int sms = sm_count();
-  if (sms <= 0) { t_last_cuda_error = (int)cudaErrorNoDevice; return CUDADMA_ERR_CUDA; }
+  const int dev = current_device();
+  if (sms <= 0 || dev < 0) { t_last_cuda_error = (int)cudaErrorNoDevice; return CUDADMA_ERR_CUDA; }
   stencil25::Coeffs k;
   for (int i = 0; i < 5; ++i) k.c[i] = coeff[i];
   const int tiles_x = (nx + stencil25::TILE_X - 1) / stencil25::TILE_X;
   const int tiles_y = (ny + stencil25::TILE_Y - 1) / stencil25::TILE_Y;
-  const int depth = z_end - z_begin;
-  if (z_chunk <= 0) {
-    /* enough CTAs for a few waves over the SMs, but runs of at least 32 planes so that the
-     * eight lead-in/lead-out planes of a run stay a small share of its loads */
-    const long long tiles = (long long)tiles_x * tiles_y;
-    const long long want = (long long)STENCIL_CTAS_TARGET * sms;
-    long long chunks = (want + tiles - 1) / tiles;
-    if (chunks < 1) chunks = 1;
-    z_chunk = (int)((depth + chunks - 1) / chunks);
-    if (z_chunk < 32) z_chunk = 32;
-    if (z_chunk > depth) z_chunk = depth;
+  const long long tiles = (long long)tiles_x * tiles_y;
+  const ChunkPlan plan = plan_chunks(z_end - z_begin, tiles, sms, z_chunk, z_edge);
+  if (plan.zc > 65535 || tiles_y > 65535) return CUDADMA_ERR_ARG;
+  if (sync.ticket) {
+    sync.boundary_ctas = boundary_ctas(plan, tiles, peer, z_begin, z_end);
+    if (sync.boundary_ctas == 0) sync = NO_SYNC;
   }
-  const int zc = (depth + z_chunk - 1) / z_chunk;
-  if (zc > 65535 || tiles_y > 65535) return CUDADMA_ERR_ARG;
-  CUtensorMap map;
-  const cuuint64_t dims[3] = {(cuuint64_t)nx, (cuuint64_t)ny, (cuuint64_t)nz};
-  const cuuint64_t strides[2] = {(cuuint64_t)nx * 4, (cuuint64_t)nx * ny * 4};
-  const cuuint32_t box[3] = {stencil25::WIN_X, stencil25::WIN_Y, 1};
-  if (int r = make_map_f32(&map, in, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, STENCIL25_L2PROMO)) return r;
-  dim3 grid(tiles_x, tiles_y, zc);
-  if (stencil25::SMEM_BYTES > 47 * 1024) {
-    static bool opted_in = false; /* dynamic shared memory above the default limit: asked for once */
-    if (!opted_in) {
-      if (int r = allow_smem(stencil25::tensor_kernel, stencil25::SMEM_BYTES)) return r;
-      opted_in = true;
-    }
+  const CUtensorMap *map = nullptr;
+  if (int r = stencil_map(&map, in, nx, ny, nz)) return r;
+  dim3 grid(tiles_x, tiles_y, plan.zc);
+  if (stencil25::SMEM_BYTES > 47 * 1024 && !g_dev[dev].stencil_smem.load()) {
+    /* dynamic shared memory above the default limit: asked for once per device */
+    if (int r = allow_smem(stencil25::tensor_kernel, stencil25::SMEM_BYTES)) return r;
+    g_dev[dev].stencil_smem.store(true);
   }
   stencil25::tensor_kernel<<<grid, stencil25::COMPUTE_THREADS + stencil25::DMA_THREADS, stencil25::SMEM_BYTES, s>>>(
-      map, out, peer, nx, ny, z_begin, z_end, z_chunk, k);
+      *map, out, peer, sync, nx, ny, z_begin, z_end, plan.z_chunk, plan.z_edge, k);
   return launched();
 }
 
@@ -299,7 +377,7 @@ int pipelined_stencil_host(float *h_out, const float *h_in, float *da, float *db
     for (int t = 1; t <= steps; ++t) {
       int reach = done[t - 1] == nz ? nz : done[t - 1] - stencil25::R;
       if (reach <= done[t]) break; /* nothing new for this step, so nothing for the later ones */
-      if (int r = launch_stencil_native(buf[t & 1], none, buf[(t - 1) & 1], nx, ny, nz, done[t], reach, coeff, 0, s)) return r;
+      if (int r = launch_stencil_native(buf[t & 1], none, NO_SYNC, buf[(t - 1) & 1], nx, ny, nz, done[t], reach, coeff, 0, 0, s)) return r;
       done[t] = reach;
     }
     if (done[steps] > down) {
@@ -325,11 +403,15 @@ int launch_gather_scatter(char *out, const char *table, const int32_t *gidx, con
   constexpr int SMEM = STAGES * 128 * RB;
   auto k = gather_scatter_kernel<RB, 128, STAGES>;
   if (int r = allow_smem(k, SMEM)) return r;
-  static int fit = 0; /* resident CTAs per SM of this instantiation, asked once */
+  const int dev = current_device();
+  if (dev < 0) { t_last_cuda_error = (int)cudaErrorNoDevice; return CUDADMA_ERR_CUDA; }
+  std::atomic<int> &slot = g_dev[dev].gather_fit[RB == 16 ? 0 : RB == 32 ? 1 : RB == 64 ? 2 : 3];
+  int fit = slot.load(); /* resident CTAs per SM of this instantiation on this device, asked once */
   if (fit == 0) {
     int f = 0;
     CK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&f, k, GS_THREADS, SMEM));
     fit = f < 1 ? 1 : f;
+    slot.store(fit);
   }
   const long long want = (long long)(fit < ctas_per_sm ? fit : ctas_per_sm) * sms;
   const int grid = (int)(nbuf < want ? nbuf : want);
@@ -338,9 +420,44 @@ int launch_gather_scatter(char *out, const char *table, const int32_t *gidx, con
 }
 }  // namespace
 
+namespace {
+/* Seeded synthetic inputs, stateless: element i is a function of seed + i (splitmix64), so a
+ * field can be made in pieces, on any device, and comes out the same everywhere. */
+__device__ __forceinline__ unsigned long long splitmix64(unsigned long long x) {
+  x += 0x9E3779B97F4A7C15ull;
+  x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+  x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+  return x ^ (x >> 31);
+}
+__global__ void fill_uniform_kernel(float *__restrict__ dst, const size_t n, const unsigned long long seed,
+                                    const float lo, const float scale) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const float u = (float)(splitmix64(seed + i) >> 40) * (1.0f / 16777216.0f);
+    dst[i] = __fadd_rn(lo, __fmul_rn(scale, u)); /* two roundings, as the host generator does it */
+  }
+}
+__global__ void fill_index_kernel(int32_t *__restrict__ dst, const size_t n, const unsigned long long seed,
+                                  const unsigned int modulo) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    dst[i] = (int32_t)(splitmix64(seed + i) % modulo);
+}
+/* One thread spins for spin_ns of wall time and reports the SM cycles and nanoseconds that
+ * passed: the SM clock under whatever runs beside it. */
+__global__ void clock_probe_kernel(unsigned long long *out, const long long spin_ns) {
+  unsigned long long t0, t1;
+  const long long c0 = clock64();
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  do {
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+  } while ((long long)(t1 - t0) < spin_ns);
+  out[0] = (unsigned long long)(clock64() - c0);
+  out[1] = t1 - t0;
+}
+}  // namespace
+
 extern "C" {
 
-int cudadma_version(void) { return 100; }
+int cudadma_version(void) { return 101; }
 
 const char *cudadma_status_string(int status) {
   switch (status) {
@@ -361,6 +478,60 @@ int cudadma_device_status(void *stream, unsigned int *out) {
   if (!out) return CUDADMA_ERR_ARG;
   CK(cudadma_b200::read_status(out, (cudaStream_t)stream));
   return CUDADMA_OK;
+}
+
+int cudadma_make_tensor_map_2d(void *out_map, const void *base, unsigned long long cols, unsigned long long rows,
+                               unsigned long long row_pitch_bytes, unsigned int box_cols, unsigned int box_rows,
+                               int swizzle_128b) {
+  if (!out_map || !base || cols == 0 || rows == 0 || box_cols == 0 || box_rows == 0 || box_cols > 256 || box_rows > 256 ||
+      !aligned16(base) || (row_pitch_bytes & 15) || row_pitch_bytes < cols * 4 || ((box_cols * 4) & 15) ||
+      (swizzle_128b && box_cols * 4 > 128))
+    return CUDADMA_ERR_ARG;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {row_pitch_bytes};
+  const cuuint32_t box[2] = {box_cols, box_rows};
+  return make_map_f32(static_cast<CUtensorMap *>(out_map), base, 2, dims, strides, box,
+                      swizzle_128b ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE);
+}
+
+int cudadma_make_tensor_map_3d(void *out_map, const void *base, unsigned long long nx, unsigned long long ny,
+                               unsigned long long nz, unsigned long long row_pitch_bytes,
+                               unsigned long long plane_pitch_bytes, unsigned int box_x, unsigned int box_y,
+                               unsigned int box_z) {
+  if (!out_map || !base || nx == 0 || ny == 0 || nz == 0 || box_x == 0 || box_y == 0 || box_z == 0 || box_x > 256 ||
+      box_y > 256 || box_z > 256 || !aligned16(base) || (row_pitch_bytes & 15) || (plane_pitch_bytes & 15) ||
+      row_pitch_bytes < nx * 4 || plane_pitch_bytes < row_pitch_bytes * ny || ((box_x * 4) & 15))
+    return CUDADMA_ERR_ARG;
+  const cuuint64_t dims[3] = {nx, ny, nz};
+  const cuuint64_t strides[2] = {row_pitch_bytes, plane_pitch_bytes};
+  const cuuint32_t box[3] = {box_x, box_y, box_z};
+  return make_map_f32(static_cast<CUtensorMap *>(out_map), base, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+}
+
+int cudadma_fill_uniform(float *dst, size_t n, unsigned long long seed, unsigned long long first_index, float lo,
+                         float hi, void *stream) {
+  if (!dst && n) return CUDADMA_ERR_ARG;
+  if (n == 0) return CUDADMA_OK;
+  const int sms = sm_count();
+  if (sms <= 0) { t_last_cuda_error = (int)cudaErrorNoDevice; return CUDADMA_ERR_CUDA; }
+  fill_uniform_kernel<<<8 * sms, 256, 0, (cudaStream_t)stream>>>(dst, n, seed + first_index, lo, hi - lo);
+  return launched();
+}
+
+int cudadma_fill_index(int32_t *dst, size_t n, unsigned long long seed, unsigned long long first_index,
+                       unsigned int modulo, void *stream) {
+  if ((!dst && n) || modulo == 0 || modulo > 0x80000000u) return CUDADMA_ERR_ARG;
+  if (n == 0) return CUDADMA_OK;
+  const int sms = sm_count();
+  if (sms <= 0) { t_last_cuda_error = (int)cudaErrorNoDevice; return CUDADMA_ERR_CUDA; }
+  fill_index_kernel<<<8 * sms, 256, 0, (cudaStream_t)stream>>>(dst, n, seed + first_index, modulo);
+  return launched();
+}
+
+int cudadma_clock_probe(unsigned long long *out, long long spin_ns, void *stream) {
+  if (!out || spin_ns <= 0 || spin_ns > 100000000ll) return CUDADMA_ERR_ARG;
+  clock_probe_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(out, spin_ns);
+  return launched();
 }
 
 int cudadma_seq_copy(void *dst, const void *src, size_t bytes, int chunk_bytes, int impl, void *stream) {
@@ -472,34 +643,45 @@ int cudadma_gather_scatter(void *out, const void *table, const int32_t *gather_i
   return CUDADMA_OK;
 }
 
-int cudadma_gather_scatter_tma(void *out, const void *table, size_t table_records, const int32_t *gather_idx,
-                               const int32_t *scatter_idx, size_t n, int record_bytes, void *stream) {
+int cudadma_gather_scatter_tma(void *out, size_t out_records, const void *table, size_t table_records,
+                               const int32_t *gather_idx, const int32_t *scatter_idx, size_t n, int record_bytes,
+                               int mode, void *stream) {
   using namespace cudadma_b200::kernels;
   if (!out || !table || !gather_idx || !scatter_idx || record_bytes != 32 || (n % 128) || table_records == 0 ||
-      table_records > 0x7fffffffull || !aligned16(out) || !aligned16(table) || !aligned16(gather_idx) ||
-      !aligned16(scatter_idx))
+      table_records > 0x7fffffffull || out_records == 0 || out_records > 0x7fffffffull || mode < 1 || mode > 3 ||
+      !aligned16(out) || !aligned16(table) || !aligned16(gather_idx) || !aligned16(scatter_idx))
     return CUDADMA_ERR_ARG;
   if (n == 0) return CUDADMA_OK;
   cudaStream_t s = (cudaStream_t)stream;
   const int sms = sm_count();
   if (sms <= 0) { t_last_cuda_error = (int)cudaErrorNoDevice; return CUDADMA_ERR_CUDA; }
   const long long nbuf = (long long)(n / 128);
-  /* the table as a 2-D tensor [records][8 floats] whose box is one record: each TMA instruction
-   * of the gather object names four records */
-  CUtensorMap map;
-  const cuuint64_t dims[2] = {8, (cuuint64_t)table_records};
+  /* table and output as 2-D tensors [records][8 floats] whose box is one record: each TMA
+   * instruction of the gather (scatter) object names four records */
+  CUtensorMap tmap, omap;
+  const cuuint64_t tdims[2] = {8, (cuuint64_t)table_records}, odims[2] = {8, (cuuint64_t)out_records};
   const cuuint64_t strides[1] = {32};
   const cuuint32_t box[2] = {8, 1};
-  if (int r = make_map_f32(&map, table, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE,
-                           CU_TENSOR_MAP_L2_PROMOTION_NONE))
+  if (int r = make_map_f32(&tmap, table, 2, tdims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE))
+    return r;
+  if (int r = make_map_f32(&omap, out, 2, odims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE))
     return r;
   constexpr int STAGES = GS_STAGES;
   constexpr int SMEM = STAGES * 128 * 32;
-  auto k = gather4_scatter_kernel<32, 128, STAGES>;
-  if (int r = allow_smem(k, SMEM)) return r;
   const long long want = (long long)GS_CTAS_PER_SM * sms;
   const int grid = (int)(nbuf < want ? nbuf : want);
-  k<<<grid, GS_THREADS, SMEM, s>>>(map, static_cast<char *>(out), gather_idx, scatter_idx, nbuf);
+  char *o = static_cast<char *>(out);
+  const char *t = static_cast<const char *>(table);
+#define CUDADMA_LAUNCH_G4S4(G4, S4)                                                                     \
+  do {                                                                                                  \
+    auto k = gather4_scatter_kernel<32, 128, STAGES, G4, S4>;                                           \
+    if (int r = allow_smem(k, SMEM)) return r;                                                          \
+    k<<<grid, GS_THREADS, SMEM, s>>>(tmap, omap, o, t, gather_idx, scatter_idx, nbuf);                  \
+  } while (0)
+  if (mode == 1) CUDADMA_LAUNCH_G4S4(true, false);
+  else if (mode == 2) CUDADMA_LAUNCH_G4S4(false, true);
+  else CUDADMA_LAUNCH_G4S4(true, true);
+#undef CUDADMA_LAUNCH_G4S4
   return launched();
 }
 
@@ -515,7 +697,8 @@ int cudadma_stencil25_step(float *out, const float *in, int nx, int ny, int nz, 
   if (impl == CUDADMA_IMPL_PORTABLE)
     return portable_stencil(const_cast<float *>(in), out, nx, ny, nz, z_begin, z_end, coeff, 1, z_chunk, s);
   if (impl != CUDADMA_IMPL_NATIVE) return CUDADMA_ERR_UNSUPPORTED;
-  return launch_stencil_native(out, stencil25::Peers{nullptr, 0, nullptr, 0}, in, nx, ny, nz, z_begin, z_end, coeff, z_chunk, s);
+  return launch_stencil_native(out, stencil25::Peers{nullptr, 0, nullptr, 0}, NO_SYNC, in, nx, ny, nz, z_begin, z_end, coeff,
+                               z_chunk, 0, s);
 }
 
 int cudadma_stencil25_run(float *a, float *b, int nx, int ny, int nz, const float coeff[5], int steps, int impl,
@@ -564,49 +747,25 @@ struct SlabHandles {            /* what a rank publishes to its z-neighbours */
   int nzl;
 };
 
+constexpr long long SLAB_WAIT_LIMIT_CYCLES = 1ll << 32; /* about two seconds */
+constexpr int SLAB_EDGE_PLANES = 32;                    /* depth of the two boundary runs of a slab step */
+
 struct Slab {
+  int device;
   int nx, ny, nzl;
   bool has_lo, has_hi;
   float *buf[2];                /* (nzl + 8) planes each: four ghost planes, the owned planes, four ghost planes */
-  unsigned int *flags;          /* [0] steps finished by the lower neighbour, [1] by the upper one (they write) */
-  float *lo_buf[2], *hi_buf[2]; /* the neighbours' arrays, mapped into this process */
+  unsigned int *flags;          /* [0] steps finished by the lower neighbour, [1] by the upper one (they write);
+                                   [2] ticket of the boundary CTAs; [3] this rank's failure word */
+  float *lo_buf[2], *hi_buf[2]; /* the neighbours' arrays, mapped into this process (or theirs, same process) */
   unsigned int *lo_flags, *hi_flags;
+  bool lo_ipc, hi_ipc;          /* mapped with CUDA IPC (to be closed), or plain pointers of this process */
   int nzl_lo;                   /* planes the lower neighbour owns */
   int cur;                      /* buf[cur] holds the current field */
   unsigned int step;            /* steps finished */
+  long long wait_limit;         /* SM cycles a boundary CTA waits for a neighbour */
+  bool failed;                  /* a failure word was read back: no further steps */
 };
-
-constexpr long long SLAB_WAIT_LIMIT_CYCLES = 1ll << 32; /* about two seconds */
-
-/* One thread waits until both neighbours have finished `need` steps. Their flag words live in
- * this GPU's memory and are written from the other GPUs, hence the system-scope loads. The wait
- * is bounded: on expiry it records a code in the status word and lets the step go on. */
-__global__ void slab_wait_kernel(const unsigned int *flag_lo, const unsigned int *flag_hi, const unsigned int need) {
-  const unsigned int *flags[2] = {flag_lo, flag_hi};
-  for (int i = 0; i < 2; ++i) {
-    if (!flags[i]) continue;
-    const long long t0 = clock64();
-    for (;;) {
-      unsigned int v;
-      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags[i]) : "memory");
-      if (v >= need) break;
-      if (clock64() - t0 > SLAB_WAIT_LIMIT_CYCLES) {
-        atomicCAS(&cudadma_b200::g_status_word, 0u, 0x80000000u | 0xE000u | (unsigned)i);
-        break;
-      }
-      __nanosleep(200);
-    }
-  }
-}
-
-/* Tells both neighbours that this rank has finished `value` steps: everything the earlier kernels
- * of the stream wrote (its own planes and the copies pushed into the neighbours' ghost planes)
- * is ordered before the flag by the system-scope fence and release store. */
-__global__ void slab_signal_kernel(unsigned int *peer_lo, unsigned int *peer_hi, const unsigned int value) {
-  __threadfence_system();
-  if (peer_lo) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peer_lo), "r"(value) : "memory");
-  if (peer_hi) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peer_hi), "r"(value) : "memory");
-}
 
 }  // namespace
 
@@ -614,9 +773,13 @@ extern "C" {
 
 int cudadma_slab_create(void **out, int nx, int ny, int nzl, int has_lower, int has_upper) {
   if (!out || nx <= 0 || ny <= 0 || (nx & 3) || nzl <= 0 || ((has_lower || has_upper) && nzl < 8)) return CUDADMA_ERR_ARG;
+  const int dev = current_device();
+  if (dev < 0) { t_last_cuda_error = (int)cudaErrorNoDevice; return CUDADMA_ERR_CUDA; }
   Slab *sl = new Slab();
+  sl->device = dev;
   sl->nx = nx; sl->ny = ny; sl->nzl = nzl;
   sl->has_lo = has_lower != 0; sl->has_hi = has_upper != 0;
+  sl->wait_limit = SLAB_WAIT_LIMIT_CYCLES;
   const size_t bytes = (size_t)nx * ny * (nzl + 8) * sizeof(float);
   cudaError_t e = cudaMalloc(&sl->buf[0], bytes);
   if (e == cudaSuccess) e = cudaMalloc(&sl->buf[1], bytes);
@@ -661,6 +824,7 @@ int cudadma_slab_connect(void *slab, const void *lower_handles, const void *uppe
     CK(cudaIpcOpenMemHandle((void **)&sl->lo_buf[1], h.buf[1], cudaIpcMemLazyEnablePeerAccess));
     CK(cudaIpcOpenMemHandle((void **)&sl->lo_flags, h.flags, cudaIpcMemLazyEnablePeerAccess));
     sl->nzl_lo = h.nzl;
+    sl->lo_ipc = true;
   }
   if (sl->has_hi) {
     SlabHandles h;
@@ -668,7 +832,48 @@ int cudadma_slab_connect(void *slab, const void *lower_handles, const void *uppe
     CK(cudaIpcOpenMemHandle((void **)&sl->hi_buf[0], h.buf[0], cudaIpcMemLazyEnablePeerAccess));
     CK(cudaIpcOpenMemHandle((void **)&sl->hi_buf[1], h.buf[1], cudaIpcMemLazyEnablePeerAccess));
     CK(cudaIpcOpenMemHandle((void **)&sl->hi_flags, h.flags, cudaIpcMemLazyEnablePeerAccess));
+    sl->hi_ipc = true;
   }
+  return CUDADMA_OK;
+}
+
+int cudadma_slab_connect_local(void *slab, void *lower_slab, void *upper_slab) {
+  Slab *sl = static_cast<Slab *>(slab);
+  Slab *lo = static_cast<Slab *>(lower_slab), *hi = static_cast<Slab *>(upper_slab);
+  if (!sl || (sl->has_lo && !lo) || (sl->has_hi && !hi)) return CUDADMA_ERR_ARG;
+  if ((sl->has_lo && (lo->nx != sl->nx || lo->ny != sl->ny)) || (sl->has_hi && (hi->nx != sl->nx || hi->ny != sl->ny)))
+    return CUDADMA_ERR_ARG;
+  int before = -1;
+  CK(cudaGetDevice(&before));
+  CK(cudaSetDevice(sl->device));
+  Slab *nb[2] = {sl->has_lo ? lo : nullptr, sl->has_hi ? hi : nullptr};
+  for (int i = 0; i < 2; ++i) {
+    if (!nb[i] || nb[i]->device == sl->device) continue;
+    int can = 0;
+    cudaError_t e = cudaDeviceCanAccessPeer(&can, sl->device, nb[i]->device);
+    if (e == cudaSuccess && !can) e = cudaErrorPeerAccessUnsupported;
+    if (e == cudaSuccess) {
+      e = cudaDeviceEnablePeerAccess(nb[i]->device, 0);
+      if (e == cudaErrorPeerAccessAlreadyEnabled) { e = cudaSuccess; cudaGetLastError(); }
+    }
+    if (e != cudaSuccess) { t_last_cuda_error = (int)e; cudaSetDevice(before); return CUDADMA_ERR_CUDA; }
+  }
+  if (sl->has_lo) {
+    sl->lo_buf[0] = lo->buf[0]; sl->lo_buf[1] = lo->buf[1]; sl->lo_flags = lo->flags; sl->nzl_lo = lo->nzl;
+    sl->lo_ipc = false;
+  }
+  if (sl->has_hi) {
+    sl->hi_buf[0] = hi->buf[0]; sl->hi_buf[1] = hi->buf[1]; sl->hi_flags = hi->flags;
+    sl->hi_ipc = false;
+  }
+  CK(cudaSetDevice(before));
+  return CUDADMA_OK;
+}
+
+int cudadma_slab_set_wait_limit(void *slab, long long sm_cycles) {
+  Slab *sl = static_cast<Slab *>(slab);
+  if (!sl || sm_cycles <= 0) return CUDADMA_ERR_ARG;
+  sl->wait_limit = sm_cycles;
   return CUDADMA_OK;
 }
 
@@ -682,44 +887,209 @@ int cudadma_slab_buffer(void *slab, int which, float **ptr) {
 int cudadma_slab_step(void *slab, const float coeff[5], void *stream) {
   Slab *sl = static_cast<Slab *>(slab);
   if (!sl || !coeff) return CUDADMA_ERR_ARG;
+  if (sl->failed) return CUDADMA_ERR_TIMEOUT;
   cudaStream_t s = (cudaStream_t)stream;
   const int nx = sl->nx, ny = sl->ny, nzl = sl->nzl, nzt = nzl + 8;
   const long long pz = (long long)nx * ny;
   float *cur = sl->buf[sl->cur], *nxt = sl->buf[sl->cur ^ 1];
   const int first = 4, last = 4 + nzl;
-  if (sl->has_lo || sl->has_hi) {
-    /* neighbours must have finished the previous step: their copies of it are in this rank's ghost
-     * planes, and they no longer read the ghost planes this step is about to overwrite */
-    slab_wait_kernel<<<1, 1, 0, s>>>(sl->has_lo ? sl->flags + 0 : nullptr, sl->has_hi ? sl->flags + 1 : nullptr,
-                                     sl->step);
-    if (int r = launched()) return r;
-  }
-  /* one launch for all owned planes; the first and last four are stored twice, here and in the
+  /* One launch for all owned planes. The first and last four are stored twice, here and in the
    * neighbour's ghost planes: plane z of this rank is plane z + nzl_lo of the lower neighbour
-   * (its upper ghost planes) and plane z - nzl of the upper neighbour (its lower ghost planes) */
+   * (its upper ghost planes) and plane z - nzl of the upper neighbour (its lower ghost planes).
+   * The CTAs at a shared boundary first wait until that neighbour has finished the previous step
+   * (its copies of it are in this rank's ghost planes, and it no longer reads the ghost planes
+   * this step overwrites); the last of them to finish publishes this rank's step count. */
   stencil25::Peers peer = {nullptr, 0, nullptr, 0};
+  stencil25::Sync sync = NO_SYNC;
   if (sl->has_lo) { peer.lo = sl->lo_buf[sl->cur ^ 1] + (long long)sl->nzl_lo * pz; peer.lo_end = first + 4; }
   if (sl->has_hi) { peer.hi = sl->hi_buf[sl->cur ^ 1] - (long long)nzl * pz; peer.hi_begin = last - 4; }
-  if (int r = launch_stencil_native(nxt, peer, cur, nx, ny, nzt, first, last, coeff, 0, s)) return r;
   if (sl->has_lo || sl->has_hi) {
-    slab_signal_kernel<<<1, 1, 0, s>>>(sl->has_lo ? sl->lo_flags + 1 : nullptr, sl->has_hi ? sl->hi_flags + 0 : nullptr,
-                                       sl->step + 1);
-    if (int r = launched()) return r;
+    sync.wait_lo = sl->has_lo ? sl->flags + 0 : nullptr;
+    sync.wait_hi = sl->has_hi ? sl->flags + 1 : nullptr;
+    sync.signal_lo = sl->has_lo ? sl->lo_flags + 1 : nullptr;
+    sync.signal_hi = sl->has_hi ? sl->hi_flags + 0 : nullptr;
+    sync.ticket = sl->flags + 2;
+    sync.failed = sl->flags + 3;
+    sync.step = sl->step;
+    sync.wait_limit = sl->wait_limit;
   }
+  if (int r = launch_stencil_native(nxt, peer, sync, cur, nx, ny, nzt, first, last, coeff, 0,
+                                    (sl->has_lo || sl->has_hi) ? SLAB_EDGE_PLANES : 0, s))
+    return r;
   sl->cur ^= 1;
   sl->step += 1;
   return CUDADMA_OK;
 }
 
+int cudadma_slab_status(void *slab, void *stream) {
+  Slab *sl = static_cast<Slab *>(slab);
+  if (!sl) return CUDADMA_ERR_ARG;
+  unsigned int w = 0;
+  CK(cudaMemcpyAsync(&w, sl->flags + 3, sizeof(w), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  CK(cudaStreamSynchronize((cudaStream_t)stream));
+  if (w != 0) sl->failed = true;
+  return sl->failed ? CUDADMA_ERR_TIMEOUT : CUDADMA_OK;
+}
+
 int cudadma_slab_destroy(void *slab) {
   Slab *sl = static_cast<Slab *>(slab);
   if (!sl) return CUDADMA_OK;
+  int before = -1;
+  cudaGetDevice(&before);
+  cudaSetDevice(sl->device);
   cudaDeviceSynchronize();
-  if (sl->has_lo) { cudaIpcCloseMemHandle(sl->lo_buf[0]); cudaIpcCloseMemHandle(sl->lo_buf[1]); cudaIpcCloseMemHandle(sl->lo_flags); }
-  if (sl->has_hi) { cudaIpcCloseMemHandle(sl->hi_buf[0]); cudaIpcCloseMemHandle(sl->hi_buf[1]); cudaIpcCloseMemHandle(sl->hi_flags); }
+  if (sl->has_lo && sl->lo_ipc) { cudaIpcCloseMemHandle(sl->lo_buf[0]); cudaIpcCloseMemHandle(sl->lo_buf[1]); cudaIpcCloseMemHandle(sl->lo_flags); }
+  if (sl->has_hi && sl->hi_ipc) { cudaIpcCloseMemHandle(sl->hi_buf[0]); cudaIpcCloseMemHandle(sl->hi_buf[1]); cudaIpcCloseMemHandle(sl->hi_flags); }
   cudaFree(sl->buf[0]); cudaFree(sl->buf[1]); cudaFree(sl->flags);
   delete sl;
   cudaGetLastError();
+  if (before >= 0) cudaSetDevice(before);
+  return CUDADMA_OK;
+}
+
+/* ---- the sharded stencil driven from one process: one slab and one stream per GPU ---- */
+
+}  /* extern "C" */
+
+namespace {
+struct Multi {
+  int n, nx, ny, nz;
+  std::vector<int> device, z_lo, z_hi;
+  std::vector<Slab *> slab;
+  std::vector<cudaStream_t> stream;   /* one per distinct device: slabs that share a GPU share its stream */
+};
+
+/* planes [lo, hi) of part r of n: as even as possible, earlier parts take the remainder */
+void even_cut(int nz, int n, int r, int *lo, int *hi) {
+  const int base = nz / n, rem = nz % n;
+  *lo = r * base + (r < rem ? r : rem);
+  *hi = *lo + base + (r < rem ? 1 : 0);
+}
+
+struct DeviceGuard {   /* puts the caller's current device back */
+  int before;
+  DeviceGuard() : before(-1) { cudaGetDevice(&before); }
+  ~DeviceGuard() { if (before >= 0) cudaSetDevice(before); }
+};
+}  // namespace
+
+extern "C" {
+
+int cudadma_stencil25_multi_destroy(void *handle) {
+  Multi *m = static_cast<Multi *>(handle);
+  if (!m) return CUDADMA_OK;
+  DeviceGuard guard;
+  for (size_t i = 0; i < m->slab.size(); ++i) {
+    if (m->stream[i]) { cudaSetDevice(m->device[i]); cudaStreamSynchronize(m->stream[i]); }
+  }
+  for (size_t i = 0; i < m->slab.size(); ++i) cudadma_slab_destroy(m->slab[i]);
+  for (size_t i = 0; i < m->stream.size(); ++i) {
+    bool first = true;
+    for (size_t j = 0; j < i; ++j) if (m->stream[j] == m->stream[i]) first = false;
+    if (first && m->stream[i]) { cudaSetDevice(m->device[i]); cudaStreamDestroy(m->stream[i]); }
+  }
+  delete m;
+  cudaGetLastError();
+  return CUDADMA_OK;
+}
+
+int cudadma_stencil25_multi_create(void **out, int n_gpus, const int *devices, int nx, int ny, int nz) {
+  if (!out || n_gpus < 1 || n_gpus > MAX_DEVICES || nx <= 0 || ny <= 0 || nz <= 0 || (nx & 3) ||
+      (n_gpus > 1 && nz / n_gpus < 8))
+    return CUDADMA_ERR_ARG;
+  DeviceGuard guard;
+  Multi *m = new Multi();
+  m->n = n_gpus; m->nx = nx; m->ny = ny; m->nz = nz;
+  int status = CUDADMA_OK;
+  for (int r = 0; r < n_gpus && status == CUDADMA_OK; ++r) {
+    const int dev = devices ? devices[r] : r;
+    int lo, hi;
+    even_cut(nz, n_gpus, r, &lo, &hi);
+    cudaError_t e = cudaSetDevice(dev);
+    if (e != cudaSuccess) { t_last_cuda_error = (int)e; status = CUDADMA_ERR_CUDA; break; }
+    void *sl = nullptr;
+    status = cudadma_slab_create(&sl, nx, ny, hi - lo, r > 0, r < n_gpus - 1);
+    if (status != CUDADMA_OK) break;
+    cudaStream_t st = nullptr;
+    for (int j = 0; j < r; ++j) if (m->device[j] == dev) st = m->stream[j];
+    if (!st) {
+      e = cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking);
+      if (e != cudaSuccess) { t_last_cuda_error = (int)e; status = CUDADMA_ERR_CUDA; cudadma_slab_destroy(sl); break; }
+    }
+    m->device.push_back(dev); m->z_lo.push_back(lo); m->z_hi.push_back(hi);
+    m->slab.push_back(static_cast<Slab *>(sl)); m->stream.push_back(st);
+  }
+  for (int r = 0; r < n_gpus && status == CUDADMA_OK; ++r)
+    status = cudadma_slab_connect_local(m->slab[r], r > 0 ? m->slab[r - 1] : nullptr, r < n_gpus - 1 ? m->slab[r + 1] : nullptr);
+  if (status != CUDADMA_OK) { cudadma_stencil25_multi_destroy(m); return status; }
+  *out = m;
+  return CUDADMA_OK;
+}
+
+int cudadma_stencil25_multi_load(void *handle, const float *h_field) {
+  Multi *m = static_cast<Multi *>(handle);
+  if (!m || !h_field) return CUDADMA_ERR_ARG;
+  DeviceGuard guard;
+  const size_t plane = (size_t)m->nx * m->ny;
+  for (int r = 0; r < m->n; ++r) {
+    Slab *sl = m->slab[r];
+    CK(cudaSetDevice(m->device[r]));
+    CK(cudaStreamSynchronize(m->stream[r]));
+    const size_t bytes = plane * (sl->nzl + 8) * sizeof(float);
+    CK(cudaMemsetAsync(sl->buf[0], 0, bytes, m->stream[r]));
+    CK(cudaMemsetAsync(sl->buf[1], 0, bytes, m->stream[r]));
+    CK(cudaMemsetAsync(sl->flags, 0, 256, m->stream[r]));
+    /* owned planes and the ghost planes that lie inside the grid, straight from the whole field */
+    const int g0 = m->z_lo[r] - 4 < 0 ? 0 : m->z_lo[r] - 4, g1 = m->z_hi[r] + 4 > m->nz ? m->nz : m->z_hi[r] + 4;
+    CK(cudaMemcpyAsync(sl->buf[0] + (size_t)(g0 - (m->z_lo[r] - 4)) * plane, h_field + (size_t)g0 * plane,
+                       (size_t)(g1 - g0) * plane * sizeof(float), cudaMemcpyHostToDevice, m->stream[r]));
+    sl->cur = 0; sl->step = 0; sl->failed = false;
+  }
+  for (int r = 0; r < m->n; ++r) { CK(cudaSetDevice(m->device[r])); CK(cudaStreamSynchronize(m->stream[r])); }
+  return CUDADMA_OK;
+}
+
+int cudadma_stencil25_multi_run(void *handle, const float coeff[5], int steps) {
+  Multi *m = static_cast<Multi *>(handle);
+  if (!m || !coeff || steps < 0) return CUDADMA_ERR_ARG;
+  DeviceGuard guard;
+  for (int t = 0; t < steps; ++t)
+    for (int r = 0; r < m->n; ++r) {
+      CK(cudaSetDevice(m->device[r]));
+      if (int e = cudadma_slab_step(m->slab[r], coeff, m->stream[r])) return e;
+    }
+  int status = CUDADMA_OK;
+  for (int r = 0; r < m->n; ++r) {
+    CK(cudaSetDevice(m->device[r]));
+    const int e = cudadma_slab_status(m->slab[r], m->stream[r]);
+    const int w = finish_status(m->stream[r]); /* waits inside the objects (the device's status word) */
+    if (e != CUDADMA_OK && status == CUDADMA_OK) status = e;
+    if (w != CUDADMA_OK && status == CUDADMA_OK) status = w;
+  }
+  return status;
+}
+
+int cudadma_stencil25_multi_store(void *handle, float *h_field) {
+  Multi *m = static_cast<Multi *>(handle);
+  if (!m || !h_field) return CUDADMA_ERR_ARG;
+  DeviceGuard guard;
+  const size_t plane = (size_t)m->nx * m->ny;
+  for (int r = 0; r < m->n; ++r) {
+    Slab *sl = m->slab[r];
+    CK(cudaSetDevice(m->device[r]));
+    CK(cudaMemcpyAsync(h_field + (size_t)m->z_lo[r] * plane, sl->buf[sl->cur] + 4 * plane,
+                       (size_t)sl->nzl * plane * sizeof(float), cudaMemcpyDeviceToHost, m->stream[r]));
+  }
+  for (int r = 0; r < m->n; ++r) { CK(cudaSetDevice(m->device[r])); CK(cudaStreamSynchronize(m->stream[r])); }
+  return CUDADMA_OK;
+}
+
+int cudadma_stencil25_multi_slab(void *handle, int rank, void **slab, int *z_lo, int *z_hi) {
+  Multi *m = static_cast<Multi *>(handle);
+  if (!m || rank < 0 || rank >= m->n) return CUDADMA_ERR_ARG;
+  if (slab) *slab = m->slab[rank];
+  if (z_lo) *z_lo = m->z_lo[rank];
+  if (z_hi) *z_hi = m->z_hi[rank];
   return CUDADMA_OK;
 }
 

@@ -183,15 +183,18 @@ transpose_kernel(const __grid_constant__ CUtensorMap in_map, float *__restrict__
 }
 
 /* ------------------------------------------------------------------------ */
-/* Indirect with TMA row gathers: the gather object fetches four table records */
-/* per cp.async.bulk.tensor ... tile::gather4 instruction through a tensor map  */
-/* of the table; bridge and scatter sides are those of gather_scatter_kernel.   */
+/* Indirect with TMA row gathers and / or row scatters: with G4 the gather      */
+/* object fetches four table records per cp.async.bulk.tensor ... tile::gather4 */
+/* instruction through a tensor map of the table, with S4 the scatter object     */
+/* writes four records per ... tile::scatter4 instruction through a tensor map   */
+/* of the output; the side without its flag works as in gather_scatter_kernel,   */
+/* whose bridge is used unchanged.                                               */
 /* ------------------------------------------------------------------------ */
-template <int RECORD_BYTES, int RECORDS, int STAGES>
+template <int RECORD_BYTES, int RECORDS, int STAGES, bool G4, bool S4>
 __global__ void __launch_bounds__(GS_THREADS)
-gather4_scatter_kernel(const __grid_constant__ CUtensorMap table_map, char *__restrict__ out,
-                       const int *__restrict__ gather_idx, const int *__restrict__ scatter_idx,
-                       const long long nbuffers) {
+gather4_scatter_kernel(const __grid_constant__ CUtensorMap table_map, const __grid_constant__ CUtensorMap out_map,
+                       char *__restrict__ out, const char *__restrict__ table, const int *__restrict__ gather_idx,
+                       const int *__restrict__ scatter_idx, const long long nbuffers) {
   extern __shared__ __align__(128) unsigned char smem[];
   constexpr int BUF = RECORD_BYTES * RECORDS;
   typedef CudaDMAIndirect<true, true, 16, 64, RECORD_BYTES, GS_GATHER_THREADS, RECORDS> Gather;
@@ -205,7 +208,8 @@ gather4_scatter_kernel(const __grid_constant__ CUtensorMap table_map, char *__re
       for (int s = 0; s < STAGES; ++s) {
         const long long b = b0 + s * stride;
         if (b >= nbuffers) return;
-        g.stage[s].execute_dma_gather4(&table_map, gather_idx + b * RECORDS, smem + s * BUF);
+        if (G4) g.stage[s].execute_dma_gather4(&table_map, gather_idx + b * RECORDS, smem + s * BUF);
+        else g.stage[s].execute_dma(gather_idx + b * RECORDS, table, smem + s * BUF);
       }
     }
   } else if (sc.stage[0].owns_this_thread()) {
@@ -214,7 +218,8 @@ gather4_scatter_kernel(const __grid_constant__ CUtensorMap table_map, char *__re
       for (int s = 0; s < STAGES; ++s) {
         const long long b = b0 + s * stride;
         if (b >= nbuffers) return;
-        sc.stage[s].execute_dma(scatter_idx + b * RECORDS, smem + s * BUF, out);
+        if (S4) sc.stage[s].execute_dma_scatter4(&out_map, scatter_idx + b * RECORDS, smem + s * BUF);
+        else sc.stage[s].execute_dma(scatter_idx + b * RECORDS, smem + s * BUF, out);
       }
     }
   } else {

@@ -57,6 +57,25 @@ struct Peers {
   float *lo; int lo_end;
   float *hi; int hi_begin;
 };
+/* Handshake of a z-sharded rank with its neighbours, folded into the step's one launch (all null:
+ * none). Flag words count finished steps. wait_lo / wait_hi live in this GPU's memory and are
+ * written by the neighbours; signal_lo / signal_hi live in the neighbours' memory. Only the CTAs
+ * at a shared boundary take part: they read the ghost planes a neighbour filled during its last
+ * step and they store into the neighbour's ghost planes, so before their first load they wait
+ * (bounded) until that neighbour's flag has reached `step`, and the last of them to retire
+ * (ticket counts them, `boundary_ctas` in all) publishes step + 1. The wait gives up after
+ * `wait_limit` SM cycles: it then records a code in the status word, nothing more is stored into a
+ * neighbour and the step count is not published, so the neighbours' own waits run out too instead
+ * of taking over a wrong plane. */
+struct Sync {
+  const unsigned int *wait_lo, *wait_hi;
+  unsigned int *signal_lo, *signal_hi;
+  unsigned int *ticket;
+  unsigned int *failed;      /* this rank's sticky failure word (0 = fine) */
+  unsigned int step;
+  unsigned int boundary_ctas;
+  long long wait_limit;
+};
 
 /* Arithmetic is done two points at a time with the packed fp32 FMA of sm_100
  * (fma.rn.f32x2 through __ffma2_rn): one issue slot for two fused multiply-adds,
@@ -158,8 +177,9 @@ __device__ __forceinline__ void fold_plane(const float *__restrict__ win, float2
  * peer.hi_begin on are stored a second time through peer.lo / peer.hi. */
 template <bool PUSH, typename RING>
 __device__ __forceinline__ void compute_side(RING &ring, const unsigned char *smem, float *__restrict__ out,
-                                             const Peers &peer, const int nx, const int ny, const int x0,
-                                             const int y0, const int z0, const int depth, const Coeffs &k) {
+                                             const Peers &peer, const Sync &sync, const int nx, const int ny,
+                                             const int x0, const int y0, const int z0, const int depth,
+                                             const Coeffs &k) {
   const int nplanes = depth + 2 * R;
   const int tx = threadIdx.x % (TILE_X / 4), ty = threadIdx.x / (TILE_X / 4);
   const long long py = nx, pz = (long long)nx * ny;
@@ -201,11 +221,13 @@ __device__ __forceinline__ void compute_side(RING &ring, const unsigned char *sm
     /* Second destinations. Kept out of the plane loop, which is tight on registers: every thread
      * reads back the cells it has just stored itself (its own stores are visible to it, and
      * still in cache) for the few planes of this CTA that lie in a pushed range, and stores
-     * them again through the peer pointer. */
+     * them again through the peer pointer. Not after a wait of the grid has given up: what this
+     * CTA computed may then rest on planes that never arrived. */
+    const bool sound = *reinterpret_cast<volatile unsigned int *>(&cudadma_b200::g_status_word) == 0u;
 #pragma unroll 1
     for (int side = 0; side < 2; ++side) {
       float *const pb = side ? peer.hi : peer.lo;
-      if (!pb) continue;
+      if (!pb || !sound) continue;
       const int zb = side ? (peer.hi_begin > z0 ? peer.hi_begin : z0) : z0;
       const int ze = side ? z0 + depth : (peer.lo_end < z0 + depth ? peer.lo_end : z0 + depth);
 #pragma unroll 1
@@ -215,31 +237,101 @@ __device__ __forceinline__ void compute_side(RING &ring, const unsigned char *sm
         if (row1_ok) *reinterpret_cast<float4 *>(pb + cell0 + plane + py) = *reinterpret_cast<const float4 *>(o + plane + py);
       }
     }
+    if (sync.ticket) {
+      /* This CTA is done with the ghost planes and with its stores into the neighbours. All its
+       * compute threads meet at a hardware barrier (id 1; the objects use mbarriers); thread 0 then
+       * makes their stores visible system-wide (the fence is cumulative over what the barrier
+       * ordered before it) and takes a ticket; the last boundary CTA of the launch publishes. */
+      asm volatile("bar.sync 1, %0;" ::"n"(COMPUTE_THREADS) : "memory");
+      if (threadIdx.x == 0) {
+        __threadfence_system();
+        const unsigned int t = atomicAdd(sync.ticket, 1u);
+        if (t + 1u == sync.boundary_ctas) {
+          *sync.ticket = 0u; /* for the next launch, which the stream orders after this one */
+          __threadfence_system();
+          const unsigned int w = *reinterpret_cast<volatile unsigned int *>(&cudadma_b200::g_status_word);
+          if (w != 0u) {
+            atomicCAS(sync.failed, 0u, w);
+          } else if (*reinterpret_cast<volatile unsigned int *>(sync.failed) == 0u) {
+            const unsigned int done = sync.step + 1u;
+            if (sync.signal_lo) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(sync.signal_lo), "r"(done) : "memory");
+            if (sync.signal_hi) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(sync.signal_hi), "r"(done) : "memory");
+          }
+        }
+      }
+    }
   }
 }
 
+/* DMA side of a boundary CTA, before its first load: wait until the neighbour on that side has
+ * finished `step` steps (see Sync). One lane polls with system-scope acquire loads; the fence
+ * afterwards orders the TMA loads of the ghost planes (asynchronous proxy) behind the acquire. */
+__device__ __noinline__ void poll_neighbour(const unsigned int *flag, const Sync &sync, const unsigned int side) {
+  const long long t0 = clock64();
+  for (;;) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v >= sync.step) return;
+    if (*reinterpret_cast<volatile unsigned int *>(&cudadma_b200::g_status_word) != 0u ||
+        *reinterpret_cast<volatile unsigned int *>(sync.failed) != 0u)
+      return; /* the step is lost already: do not sit out another limit */
+    if (clock64() - t0 > sync.wait_limit) {
+      atomicCAS(&cudadma_b200::g_status_word, 0u, 0x80000000u | 0xE000u | side);
+      return;
+    }
+    __nanosleep(100);
+  }
+}
+__device__ __forceinline__ void wait_for_neighbours(const Sync &sync, const bool lo, const bool hi) {
+  if ((threadIdx.x & 31) == 0) {
+    if (lo && sync.wait_lo) poll_neighbour(sync.wait_lo, sync, 0u);
+    if (hi && sync.wait_hi) poll_neighbour(sync.wait_hi, sync, 1u);
+    asm volatile("fence.proxy.async;" ::: "memory");
+  }
+  __syncwarp();
+}
+
 /* in_map: 3-D tensor map over the nx x ny x nz input (x fastest), box 40 x 40 x 1.
- * Output planes [z_begin, z_end) are produced, blockIdx.z taking z_chunk of them;
- * input planes outside [0, nz) read as zero. Planes are numbered kp = 0 .. depth + 7
- * from (first output plane - 4); output plane kp - 8 is stored at step kp.
+ * Output planes [z_begin, z_end) are produced; input planes outside [0, nz) read as zero. Planes
+ * of a CTA are numbered kp = 0 .. depth + 7 from (first output plane - 4); output plane kp - 8 is
+ * stored at step kp.
+ * Runs of planes per CTA: z_edge == 0: blockIdx.z takes planes [z_begin + blockIdx.z * z_chunk, + z_chunk).
+ * z_edge > 0 (sharded ranks): blockIdx.z == 0 takes the lowest z_edge planes, blockIdx.z == 1 the
+ * highest z_edge planes, and blockIdx.z >= 2 runs of z_chunk planes of what lies between. CTAs are
+ * dispatched in blockIdx order, so both boundary runs start first and the step count can go out
+ * to the neighbours while the interior is still being computed.
  * Peers: output planes below peer.lo_end are stored a second time through peer.lo, planes from
  * peer.hi_begin on through peer.hi, at the same plane index (null pointers switch this off).
  * The sharded driver points them into the z-neighbour GPUs' ghost planes (plain stores over
- * NVLink), shifted so that this rank's plane numbers land on the neighbour's. */
+ * NVLink), shifted so that this rank's plane numbers land on the neighbour's. Sync: see above. */
 #ifndef STENCIL25_MIN_BLOCKS
 #define STENCIL25_MIN_BLOCKS 2 /* two CTAs of 160 threads per SM: eight compute warps, 167 registers */
 #endif
 __global__ void __launch_bounds__(COMPUTE_THREADS + DMA_THREADS, STENCIL25_MIN_BLOCKS)
 tensor_kernel(const __grid_constant__ CUtensorMap in_map, float *__restrict__ out, const Peers peer,
-              const int nx, const int ny, const int z_begin, const int z_end, const int z_chunk, const Coeffs k) {
+              const __grid_constant__ Sync sync, const int nx, const int ny, const int z_begin, const int z_end,
+              const int z_chunk, const int z_edge, const Coeffs k) {
   extern __shared__ __align__(128) unsigned char smem[];
   typedef CudaDMAHalo<float, R, true, 16> Halo;
   cudadma_b200::kernels::Ring<Halo, STAGES> ring(DMA_THREADS, COMPUTE_THREADS, COMPUTE_THREADS, TILE_X, TILE_Y, nx);
   const int x0 = blockIdx.x * TILE_X, y0 = blockIdx.y * TILE_Y;
-  const int z0 = z_begin + blockIdx.z * z_chunk;
-  const int depth = (z_end - z0 < z_chunk) ? (z_end - z0) : z_chunk;
+  int z0, depth;
+  if (z_edge > 0) {
+    if (blockIdx.z == 0) { z0 = z_begin; depth = z_edge; }
+    else if (blockIdx.z == 1) { z0 = z_end - z_edge; depth = z_edge; }
+    else {
+      z0 = z_begin + z_edge + ((int)blockIdx.z - 2) * z_chunk;
+      depth = (z_end - z_edge - z0 < z_chunk) ? (z_end - z_edge - z0) : z_chunk;
+    }
+  } else {
+    z0 = z_begin + blockIdx.z * z_chunk;
+    depth = (z_end - z0 < z_chunk) ? (z_end - z0) : z_chunk;
+  }
   const int nplanes = depth + 2 * R;
+  /* CTAs whose planes reach into a pushed range are the ones that touch a shared boundary */
+  const bool at_lo = peer.lo && z0 < peer.lo_end, at_hi = peer.hi && z0 + depth > peer.hi_begin;
   if (ring.stage[0].owns_this_thread()) {
+    if ((at_lo || at_hi) && sync.ticket) wait_for_neighbours(sync, at_lo, at_hi);
     for (int k0 = 0;; k0 += STAGES) {
 #pragma unroll
       for (int s = 0; s < STAGES; ++s) {
@@ -248,11 +340,10 @@ tensor_kernel(const __grid_constant__ CUtensorMap in_map, float *__restrict__ ou
       }
     }
   } else {
-    /* Only CTAs whose planes reach into a pushed range run the instantiation with the second
-     * stores behind its loop (one body for all measured 1 % slower without peers). */
-    const bool pushes = (peer.lo && z0 < peer.lo_end) || (peer.hi && z0 + depth > peer.hi_begin);
-    if (pushes) compute_side<true>(ring, smem, out, peer, nx, ny, x0, y0, z0, depth, k);
-    else compute_side<false>(ring, smem, out, peer, nx, ny, x0, y0, z0, depth, k);
+    /* Only those CTAs run the instantiation with the second stores behind its loop (one body for
+     * all measured 1 % slower without peers). */
+    if (at_lo || at_hi) compute_side<true>(ring, smem, out, peer, sync, nx, ny, x0, y0, z0, depth, k);
+    else compute_side<false>(ring, smem, out, peer, sync, nx, ny, x0, y0, z0, depth, k);
   }
 }
 #endif

@@ -15,12 +15,13 @@ One step, exchange = "nccl":
      send/recv: NCCL over NVLink on GPUs) on a side stream;
   3. the remaining interior planes are computed meanwhile on the main stream;
   4. the main stream joins the exchange, buffers swap.
-One step, exchange = "p2p" (CUDA devices only): one kernel launch computes all
-owned planes and stores the first and last four a second time, into the
+One step, exchange = "p2p" (CUDA devices only): ONE kernel launch. Its CTAs at
+a shared boundary wait (bounded) for the neighbour's step count, all owned
+planes are computed, the first and last four stored a second time, into the
 neighbours' ghost planes over NVLink (the arrays are shared between the
-processes with CUDA IPC), and a flag word per neighbour says how many steps each
-side has finished; see cudadma_slab_step in include/cudadma_b200.h. No
-collective library on the step.
+processes with CUDA IPC), and the last boundary CTA publishes this rank's step
+count while the interior is still running; see cudadma_slab_step in
+include/cudadma_b200.h. No collective library on the step.
 Every plane is computed by the same kernel with the same arithmetic whatever
 the sharding, so an N-rank run reproduces the 1-rank field bit for bit.
 
@@ -118,8 +119,10 @@ class ShardedStencil:
         exchange_timeout: seconds a rank waits on the host for its neighbours' planes before step()
         raises ExchangeError (ranks on CPU). On CUDA devices nothing waits on the host during a
         step: a lost neighbour ends the "nccl" exchange through the process group's own timeout,
-        and the "p2p" exchange through the bounded wait of cudadma_slab_step (status
-        CUDADMA_ERR_TIMEOUT after about two seconds)."""
+        and the "p2p" exchange through the bounded wait inside cudadma_slab_step's kernel (about two
+        seconds): that rank then stops pushing planes and publishing its step count, so its
+        neighbours' waits run out in turn, and check_status() -- which run() and run_host() call --
+        raises ExchangeError on every rank."""
         self.nx, self.ny, self.nz = nx, ny, nz
         self.pad = pad_xy
         self.coeff = tuple(capi.STENCIL_COEFFS if coeff is None else coeff)
@@ -251,7 +254,30 @@ class ShardedStencil:
     def run(self, steps):
         for _ in range(steps):
             self.step()
+        if self.slab is not None:
+            self.check_status()
         return self.owned()
+
+    def check_status(self):
+        """Waits for the steps issued so far and raises ExchangeError, on every rank alike, if a
+        bounded wait inside any rank's kernels gave up (a neighbour gone or too far behind): the
+        fields are not to be trusted then. step() itself never waits on the host, so a time loop
+        calls this where it would look at its results anyway."""
+        if not self.on_cuda:
+            return
+        with torch.cuda.device(self.device):
+            bad = 0
+            if self.slab is not None and self.slab.status() != capi.OK:
+                bad = 1
+            if capi.device_status() != 0:
+                bad = 1
+        if self.distributed and self.world > 1:
+            t = torch.tensor([bad], dtype=torch.int32, device=self.device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+            bad = int(t.item())
+        if bad:
+            raise ExchangeError("rank %d: a wait for a neighbour's planes gave up on some rank by step %d"
+                                % (self.rank, self.steps_done))
 
     # -- checkpoint / restart ----------------------------------------------
     _MAGIC = b"CDB200S1"
@@ -311,8 +337,7 @@ class ShardedStencil:
             self.store(h_out)
         if self.on_cuda:
             torch.cuda.current_stream(self.device).synchronize()
-            if capi.device_status() != 0:
-                raise capi.CudaDMAError("ShardedStencil.run_host", capi.ERR_TIMEOUT, "a wait inside a kernel gave up")
+            self.check_status()
 
     def _chunk_planes(self, chunk_planes):
         if chunk_planes:

@@ -185,10 +185,6 @@ __device__ __forceinline__ void mbar_arrive_warp(uint32_t bar) {
   if ((threadIdx.x & 31u) == (unsigned)(__ffs(mask) - 1)) mbar_arrive_n(bar, (uint32_t)__popc(mask));
 #endif
 }
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-               : "memory");
-}
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");
@@ -274,6 +270,7 @@ __device__ __forceinline__ void tensor_gather4(uint32_t dst, const CUtensorMap *
       "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y0), "r"(y1), "r"(y2), "r"(y3), "r"(bar)
       : "memory");
 }
+/* TMA row scatter: four packed rows from shared memory to rows y0..y3 of a 2-D tensor (bulk group) */
 __device__ __forceinline__ void tensor_scatter4(const CUtensorMap *map, int x, int y0, int y1, int y2, int y3,
                                                 uint32_t src) {
   asm volatile(
@@ -282,20 +279,26 @@ __device__ __forceinline__ void tensor_scatter4(const CUtensorMap *map, int x, i
       "r"(x), "r"(y0), "r"(y1), "r"(y2), "r"(y3), "r"(src)
       : "memory");
 }
-__device__ __forceinline__ void tensor_s2g_2d(const CUtensorMap *map, int x, int y, uint32_t src) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
-                   reinterpret_cast<uint64_t>(map)),
-               "r"(x), "r"(y), "r"(src)
-               : "memory");
-}
-/* per-thread asynchronous copy global -> shared of UNIT = 4, 8 or 16 bytes */
-template <int UNIT, bool L2_ONLY>
+/* per-thread asynchronous copy global -> shared of UNIT = 4, 8 or 16 bytes.
+ * HALF_LINE: the copy belongs to a run of at most 64 bytes whose neighbourhood nobody wants (a
+ * gathered record). A miss then fetches 64 bytes from DRAM instead of the whole 128-byte line,
+ * which is what a load without the .L2::64B qualifier costs on this part (measured: 2^22 random
+ * 32-byte records read 533 MB of DRAM without it and 292 MB with it). */
+template <int UNIT, bool L2_ONLY, bool HALF_LINE = false>
 __device__ __forceinline__ void ldgsts(uint32_t dst, const void *src) {
-  if (UNIT == 16 && L2_ONLY)
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gmem_u64(src)) : "memory");
-  else
-    asm volatile("cp.async.ca.shared.global [%0], [%1], %2;" ::"r"(dst), "l"(gmem_u64(src)), "n"(UNIT)
-                 : "memory");
+  if (HALF_LINE) {
+    if (UNIT == 16 && L2_ONLY)
+      asm volatile("cp.async.cg.shared.global.L2::64B [%0], [%1], 16;" ::"r"(dst), "l"(gmem_u64(src)) : "memory");
+    else
+      asm volatile("cp.async.ca.shared.global.L2::64B [%0], [%1], %2;" ::"r"(dst), "l"(gmem_u64(src)), "n"(UNIT)
+                   : "memory");
+  } else {
+    if (UNIT == 16 && L2_ONLY)
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gmem_u64(src)) : "memory");
+    else
+      asm volatile("cp.async.ca.shared.global [%0], [%1], %2;" ::"r"(dst), "l"(gmem_u64(src)), "n"(UNIT)
+                   : "memory");
+  }
 }
 __device__ __forceinline__ void ldgsts_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
@@ -338,18 +341,21 @@ template <> struct unit_type<16> { typedef uint4 type; };
 
 /* Addressing of a transfer made of `rows` contiguous runs of `row_bytes`. */
 struct StridedRows {
+  static constexpr bool SCATTERED_SOURCE = false; /* rows of one array: neighbouring rows want the rest of a line */
   const char *src; char *dst; long long src_stride; long long dst_stride;
   __device__ __forceinline__ const char *src_row(int r) const { return src + (long long)r * src_stride; }
   __device__ __forceinline__ char *dst_row(int r) const { return dst + (long long)r * dst_stride; }
 };
 /* gather: row r comes from src + index[r] * row_bytes, lands at dst + r * pitch */
 struct GatherRows {
+  static constexpr bool SCATTERED_SOURCE = true;
   const char *src; char *dst; const int *index; long long row_bytes; long long pitch;
   __device__ __forceinline__ const char *src_row(int r) const { return src + (long long)__ldg(index + r) * row_bytes; }
   __device__ __forceinline__ char *dst_row(int r) const { return dst + (long long)r * pitch; }
 };
 /* scatter: row r comes from src + r * pitch, lands at dst + index[r] * row_bytes */
 struct ScatterRows {
+  static constexpr bool SCATTERED_SOURCE = false;
   const char *src; char *dst; const int *index; long long row_bytes; long long pitch;
   __device__ __forceinline__ const char *src_row(int r) const { return src + (long long)r * pitch; }
   __device__ __forceinline__ char *dst_row(int r) const { return dst + (long long)__ldg(index + r) * row_bytes; }
@@ -377,18 +383,19 @@ __device__ __forceinline__ void for_each_unit(int rows, int row_bytes, int tid, 
   }
 }
 
-/* global -> shared with per-thread cp.async in pieces of `unit` bytes */
-template <bool L2_ONLY, typename ROWS>
+/* global -> shared with per-thread cp.async in pieces of `unit` bytes. HALF_LINE: see ptx::ldgsts;
+ * set for scattered rows (gathers) of at most 64 bytes. */
+template <bool L2_ONLY, bool HALF_LINE, typename ROWS>
 __device__ __forceinline__ void ldgsts_rows(const ROWS &a, int rows, int row_bytes, int unit, int tid, int nthreads) {
   if (unit == 16)
     for_each_unit<16>(rows, row_bytes, tid, nthreads, [&](int r, int off) {
-      ptx::ldgsts<16, L2_ONLY>(ptx::smem_u32(a.dst_row(r) + off), a.src_row(r) + off); });
+      ptx::ldgsts<16, L2_ONLY, HALF_LINE>(ptx::smem_u32(a.dst_row(r) + off), a.src_row(r) + off); });
   else if (unit == 8)
     for_each_unit<8>(rows, row_bytes, tid, nthreads, [&](int r, int off) {
-      ptx::ldgsts<8, false>(ptx::smem_u32(a.dst_row(r) + off), a.src_row(r) + off); });
+      ptx::ldgsts<8, false, HALF_LINE>(ptx::smem_u32(a.dst_row(r) + off), a.src_row(r) + off); });
   else
     for_each_unit<4>(rows, row_bytes, tid, nthreads, [&](int r, int off) {
-      ptx::ldgsts<4, false>(ptx::smem_u32(a.dst_row(r) + off), a.src_row(r) + off); });
+      ptx::ldgsts<4, false, HALF_LINE>(ptx::smem_u32(a.dst_row(r) + off), a.src_row(r) + off); });
 }
 
 /* any address space -> any address space through registers (generic ld / st) */
@@ -537,11 +544,15 @@ __device__ __forceinline__ int issue_rows(const ROWS &a, const int rows, const i
       }
       return 0;
     }
-    ldgsts_rows<L2_ONLY>(a, rows, row_bytes, unit, tid, nthreads);
+    if (ROWS::SCATTERED_SOURCE && row_bytes <= 64) ldgsts_rows<L2_ONLY, true>(a, rows, row_bytes, unit, tid, nthreads);
+    else ldgsts_rows<L2_ONLY, false>(a, rows, row_bytes, unit, tid, nthreads);
     return 1;
   }
   if (__isShared(s0) && __isGlobal(d0) && unit == 16 && row_bytes >= CUDADMA_BULK_ROW_MIN) {
-    /* bulk stores; returns once shared memory has been read */
+    /* Bulk stores. The call returns once shared memory has been READ (the buffer may be refilled);
+     * the global writes complete asynchronously, at the latest at kernel end: a thread that wants
+     * to read the destination back inside the same kernel must first wait for the whole bulk
+     * group (cp.async.bulk.wait_group 0), which the reference's plain stores did not need. */
     ptx::fence_proxy_async();
     if (tid >= 0) {
       for (int r = tid; r < rows; r += nthreads)
@@ -1056,6 +1067,25 @@ class CudaDMAIndirect : public CudaDMA {
     finish_async_dma();
   }
 
+  /* Extension (scatter only): TMA row scatter. `map` describes the destination as a 2-D tensor
+   * [destination rows][row elements] whose box is one row wide; four packed rows of the shared
+   * buffer leave per instruction. Needs m_rows % 4 == 0, the index array 16-byte aligned and
+   * src 128-byte aligned, rows packed. Returns once the buffer has been read. */
+  __device__ __forceinline__ void execute_dma_scatter4(const CUtensorMap *map, const int *__restrict__ index_ptr,
+                                                       const void *src) {
+    static_assert(DO_SYNC && !GATHER, "scatter4 needs a warp-specialised scatter object");
+    wait_for_dma_start();
+    const int groups = m_rows >> 2;
+    const uint32_t s0 = cudadma_b200::ptx::smem_u32(src);
+    for (int g = m_dma_tid; g < groups; g += m_num_dma_threads) {
+      const int4 ix = __ldg(reinterpret_cast<const int4 *>(index_ptr) + g);
+      cudadma_b200::ptx::tensor_scatter4(map, 0, ix.x, ix.y, ix.z, ix.w, s0 + (uint32_t)g * 4u * (uint32_t)m_bytes);
+    }
+    cudadma_b200::ptx::bulk_commit();
+    cudadma_b200::ptx::bulk_wait_read<0>();
+    finish_async_dma();
+  }
+
  private:
   template <bool GLOBAL, int LQ>
   __device__ __forceinline__ void start_impl(const int *index, const void *src) {
@@ -1123,12 +1153,14 @@ class CudaDMAIndirect<GATHER, DO_SYNC, 0, 0, 0, 0, 0> {
 template <typename ELMT_TYPE, int RADIUS, bool CORNERS, int ALIGNMENT>
 class CudaDMAHalo : public CudaDMA {
   struct RingRows {   /* item i: rows above (i < RADIUS) then rows below */
+    static constexpr bool SCATTERED_SOURCE = false;
     const char *src; char *dst; int dimy; long long spitch, dpitch;
     __device__ __forceinline__ long long row(int i) const { return (i < RADIUS) ? (i - RADIUS) : (dimy + i - RADIUS); }
     __device__ __forceinline__ const char *src_row(int i) const { return src + row(i) * spitch; }
     __device__ __forceinline__ char *dst_row(int i) const { return dst + row(i) * dpitch; }
   };
   struct RingSides {  /* item i: row i/2, left panel (even) or right panel (odd) */
+    static constexpr bool SCATTERED_SOURCE = false;
     const char *src; char *dst; long long right; long long spitch, dpitch;
     __device__ __forceinline__ const char *src_row(int i) const { return src + (i >> 1) * spitch + ((i & 1) ? right : 0); }
     __device__ __forceinline__ char *dst_row(int i) const { return dst + (i >> 1) * dpitch + ((i & 1) ? right : 0); }

@@ -50,6 +50,40 @@ int cudadma_device_status(void *stream, unsigned int *out);
 /* Number of kernels this library has launched in this process (all calls). */
 unsigned long long cudadma_launch_count(void);
 
+/* Host side of the tensor-map extensions of the classes (CudaDMAStrided::execute_dma_tensor,
+ * CudaDMAHalo::execute_dma_tile, CudaDMAIndirect::execute_dma_gather4 / execute_dma_scatter4).
+ * The reference's constructors take their strides on the device (include/cudaDMAv2.h:8631-8651);
+ * a tensor map has to be encoded on the host and handed to the kernel as a __grid_constant__
+ * parameter, and these two calls do the encoding. out_map: 128 bytes, 64-byte aligned (a
+ * CUtensorMap). Elements are 4-byte words; reads outside the tensor give zero.
+ * 2-D: `rows` rows of `cols` words, row_pitch_bytes apart; the box is box_cols x box_rows
+ * (each at most 256, box_cols * 4 a multiple of 16); swizzle_128b != 0 asks for the 128-byte
+ * shared-memory swizzle (box_cols <= 32 then). 3-D: nx x ny x nz words, x fastest, rows
+ * row_pitch_bytes and planes plane_pitch_bytes apart; box box_x x box_y x box_z.
+ * base 16-byte aligned, pitches multiples of 16. */
+int cudadma_make_tensor_map_2d(void *out_map, const void *base, unsigned long long cols, unsigned long long rows,
+                               unsigned long long row_pitch_bytes, unsigned int box_cols, unsigned int box_rows,
+                               int swizzle_128b);
+int cudadma_make_tensor_map_3d(void *out_map, const void *base, unsigned long long nx, unsigned long long ny,
+                               unsigned long long nz, unsigned long long row_pitch_bytes,
+                               unsigned long long plane_pitch_bytes, unsigned int box_x, unsigned int box_y,
+                               unsigned int box_z);
+
+/* Seeded synthetic inputs on the device, for benchmarks and tests. (The reference fills its inputs
+ * on the host: h_idata[i] = float(i), src/tests/test_sequential/cudaDMA_test_sequential_v2.cu:417-418,
+ * or rand(), src/tests/test_halo/cudaDMA_test_halo.cu:245-246.) Element i of a field is a function of
+ * seed + first_index + i alone (splitmix64; uniform = lo + (hi - lo) * top 24 bits * 2^-24;
+ * index = value mod modulo), so a field can be produced in pieces, on any GPU, and every piece
+ * equals the same range of the whole. */
+int cudadma_fill_uniform(float *dst, size_t n, unsigned long long seed, unsigned long long first_index, float lo,
+                         float hi, void *stream);
+int cudadma_fill_index(int32_t *dst, size_t n, unsigned long long seed, unsigned long long first_index,
+                       unsigned int modulo, void *stream);
+/* Measurement aid: a one-thread kernel that spins for spin_ns nanoseconds and writes the SM cycles
+ * and the nanoseconds that passed to out[0], out[1] (device memory). Launched on a second stream
+ * beside a workload it reports the SM clock the workload actually ran at. */
+int cudadma_clock_probe(unsigned long long *out, long long spin_ns, void *stream);
+
 /* Sequential chunk copy: dst[0..bytes) = src[0..bytes), every chunk_bytes chunk
  * staged global -> shared -> global by CudaDMASequential (4 DMA + 8 compute
  * warps). Replaces the launch in src/perf/sequential/perf_sequential.cu:225-369
@@ -73,13 +107,17 @@ int cudadma_strided_transpose(float *dst, const float *src, int rows, int cols, 
 int cudadma_gather_scatter(void *out, const void *table, const int32_t *gather_idx, const int32_t *scatter_idx,
                            size_t n, int record_bytes, int impl, void *stream);
 
-/* The same workload with the gather done by TMA row gathers (cp.async.bulk.tensor ... tile::gather4
- * through CudaDMAIndirect::execute_dma_gather4): four table records per instruction. The tensor map
- * needs the table's extent, hence table_records. Same result; on B200 it measured slower than the
- * 16-byte cp.async gather of cudadma_gather_scatter (1.63 against 1.76 TB/s on the benchmark
- * configuration), so the latter stays the default path. gather_idx entries must be < table_records. */
-int cudadma_gather_scatter_tma(void *out, const void *table, size_t table_records, const int32_t *gather_idx,
-                               const int32_t *scatter_idx, size_t n, int record_bytes, void *stream);
+/* The same workload with TMA row instructions, four records each: mode bit 0 = the gather through
+ * cp.async.bulk.tensor ... tile::gather4 (CudaDMAIndirect::execute_dma_gather4), bit 1 = the scatter
+ * through ... tile::scatter4 (execute_dma_scatter4); mode 1, 2 or 3. The tensor maps need the
+ * extents of table and output, hence table_records and out_records. Same result as
+ * cudadma_gather_scatter, which stays the default path: on B200 neither TMA form was faster than
+ * its 16-byte cp.async gather and 16-byte stores (figures with the benchmark configuration are in
+ * the repository's design notes). gather_idx entries must be < table_records, scatter_idx
+ * entries < out_records; record_bytes must be 32. */
+int cudadma_gather_scatter_tma(void *out, size_t out_records, const void *table, size_t table_records,
+                               const int32_t *gather_idx, const int32_t *scatter_idx, size_t n, int record_bytes,
+                               int mode, void *stream);
 
 /* One step of the radius-4 25-point stencil on an nx x ny x nz fp32 grid (x
  * fastest), output planes [z_begin, z_end) only; reads outside the grid give
@@ -104,27 +142,59 @@ int cudadma_stencil25_run(float *a, float *b, int nx, int ny, int nz, const floa
 int cudadma_stencil25_step_padded(float *out, const float *in, int nx, int ny, int nz, int z_begin, int z_end,
                                   const float coeff[5], int z_chunk, int impl, void *stream);
 
-/* z-sharded stencil, one process per GPU, halo planes pushed straight into the z-neighbours'
- * memory. (The reference has no multi-GPU code; every program of it uses device 0,
- * src/examples/stencil/cudaDMA_stencil2D.cu:62.) A slab is this rank's nzl planes of an
- * nx x ny x nz grid plus four ghost planes on either side, in two ping-pong arrays that the
- * library allocates so that they can be shared between processes (CUDA IPC).
+/* z-sharded stencil, halo planes pushed straight into the z-neighbours' memory. (The reference has
+ * no multi-GPU code; every program of it uses device 0, src/examples/stencil/cudaDMA_stencil2D.cu:62.)
+ * A slab is one rank's nzl planes of an nx x ny x nz grid plus four ghost planes on either side,
+ * in two ping-pong arrays that the library allocates on the current device so that they can be
+ * shared between processes (CUDA IPC).
  *   create  -> export (cudadma_slab_handle_bytes() bytes to hand to both neighbours, by any
  *   means) -> connect (with the neighbours' bytes) -> fill buffer 0 (current field; ghost planes
- *   included) -> step, step, ... -> read buffer 0 -> destroy.
- * One step: wait until both neighbours have finished the previous step (a flag word they write
- * into this GPU's memory; the wait is bounded), compute all owned planes in one launch, the
- * first and last four of them stored twice, here and in the neighbour's ghost planes over
- * NVLink, then publish this rank's step count to both neighbours. No collective library is
+ *   included) -> step, step, ... -> status -> read buffer 0 -> destroy.
+ * Slabs of one process (one per GPU, or several on one GPU) are joined with
+ * cudadma_slab_connect_local instead of export / connect; it enables peer access where the
+ * slabs sit on different GPUs.
+ * One step is ONE kernel launch. The CTAs at a boundary shared with a neighbour first wait until
+ * that neighbour has finished the previous step (a flag word it writes into this GPU's memory;
+ * the wait is bounded, about two seconds unless cudadma_slab_set_wait_limit says otherwise), the
+ * first and last four owned planes are stored twice, here and in the neighbour's ghost planes over
+ * NVLink, and the last boundary CTA to finish publishes this rank's step count to both
+ * neighbours, while the interior of the slab is still being computed. No collective library is
  * involved. has_lower / has_upper say whether a neighbour exists on that side; nzl >= 8 then.
+ * When a wait runs out (a neighbour is gone or more than the limit behind), the launch records
+ * it, stores nothing more into the neighbours and does not publish its step count, so the
+ * neighbours' own waits run out as well instead of taking over wrong planes; this rank's own
+ * field is undefined from then on. cudadma_slab_status(slab, stream) synchronises the stream and
+ * returns CUDADMA_ERR_TIMEOUT if that has happened, and from then on so does every
+ * cudadma_slab_step, without launching.
  * cudadma_slab_buffer: which = 0 the current field, 1 the other array; (nzl + 8) * ny * nx floats. */
 int cudadma_slab_create(void **slab, int nx, int ny, int nzl, int has_lower, int has_upper);
 size_t cudadma_slab_handle_bytes(void);
 int cudadma_slab_export(void *slab, void *handles);
 int cudadma_slab_connect(void *slab, const void *lower_handles, const void *upper_handles);
+int cudadma_slab_connect_local(void *slab, void *lower_slab, void *upper_slab);
+int cudadma_slab_set_wait_limit(void *slab, long long sm_cycles);
 int cudadma_slab_buffer(void *slab, int which, float **ptr);
 int cudadma_slab_step(void *slab, const float coeff[5], void *stream);
+int cudadma_slab_status(void *slab, void *stream);
 int cudadma_slab_destroy(void *slab);
+
+/* The whole sharded stencil driven from ONE process: n_gpus slabs (planes split as evenly as
+ * possible, lower ranks take the remainder), one per entry of `devices` (null: devices 0 ..
+ * n_gpus - 1), one stream per GPU, neighbours joined by peer access, the step as above. A C or
+ * C++ solver links against these five calls and needs no process launcher. Entries of `devices`
+ * may repeat: slabs that share a GPU share its stream, so their steps run one after the other,
+ * each after the steps it waits for (a way to run the N-rank path on fewer GPUs).
+ * load: the whole nx x ny x nz field from host memory into the slabs, ghost planes included.
+ * run: `steps` steps on every slab; returns after all GPUs have finished, with
+ * CUDADMA_ERR_TIMEOUT if any wait gave up. store: the whole field back to host memory.
+ * slab: the slab handle and plane range [z_lo, z_hi) of one rank, for callers that fill or read
+ * device memory themselves (cudadma_slab_buffer). nz / n_gpus >= 8 for n_gpus > 1. */
+int cudadma_stencil25_multi_create(void **handle, int n_gpus, const int *devices, int nx, int ny, int nz);
+int cudadma_stencil25_multi_load(void *handle, const float *h_field);
+int cudadma_stencil25_multi_run(void *handle, const float coeff[5], int steps);
+int cudadma_stencil25_multi_store(void *handle, float *h_field);
+int cudadma_stencil25_multi_slab(void *handle, int rank, void **slab, int *z_lo, int *z_hi);
+int cudadma_stencil25_multi_destroy(void *handle);
 
 /* One stencil step for callers that must not allocate device memory. (No counterpart in the
  * reference, which has no host library at all.)
@@ -136,19 +206,26 @@ int cudadma_slab_destroy(void *slab);
  * the pool), and for a time-step loop that runs next to other streams, because cudaMalloc and
  * cudaFree stall the whole device while they work. This entry point runs the same kernel with
  * the padded copies in an array that is part of the library image instead, so it makes no
- * cudaMalloc, no cudaFree and no other allocating call, at any time.
+ * cudaMalloc, no cudaFree and no other allocating call (see the last point below for the one
+ * allocation the CUDA runtime itself makes when it loads the library's device code).
  *
  * What that costs and what to watch:
  *   - the array is 16 MiB and every GPU that loads the library carries it until the process
  *     exits, whether or not this function is ever called;
  *   - the padded grid (nx + 8) * (ny + 8) * (nz + 8) may have at most 2^21 cells (for
- *     example 120 x 112 x 120); a larger one returns CUDADMA_ERR_TOO_LARGE and touches nothing;
+ *     example 128 x 112 x 120: 136 * 120 * 128 = 2 088 960 cells); a larger one returns
+ *     CUDADMA_ERR_TOO_LARGE and touches nothing;
  *   - all calls on a GPU share the array. Each call first re-makes the zero border it needs,
  *     so the previous call's leftovers do no harm, but two calls whose work overlaps on the GPU
  *     (different streams, no ordering between them) race on it: keep them on one stream or
  *     order them with events;
  *   - the first call on each GPU looks up the array's device address (one runtime query, with
- *     that GPU current); make that first call before any stream capture begins.
+ *     that GPU current); make that first call before any stream capture begins;
+ *   - the 16 MiB are reserved when the CUDA runtime loads this library's device code on a GPU,
+ *     which it does lazily, at the library's first kernel launch or address query there. A
+ *     framework that takes all remaining device memory into its pool must therefore make one
+ *     call into this library on every GPU BEFORE it sizes that pool (any launching call will
+ *     do, this one included), or the load itself fails for lack of memory.
  * Same arguments and result as cudadma_stencil25_step(out, in, nx, ny, nz, 0, nz, coeff, 0,
  * CUDADMA_IMPL_PORTABLE, stream): nx % 32 == 0, ny % 16 == 0, pointers 16-byte aligned, in != out. */
 int cudadma_stencil25_step_noalloc(float *out, const float *in, int nx, int ny, int nz, const float coeff[5],

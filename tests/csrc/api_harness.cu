@@ -479,9 +479,65 @@ __global__ void starved_kernel(const float *idata, int ncompute, int ndma) {
 }
 #endif
 
+#ifdef HAVE_STATUS
+/* CudaDMACustom (v1 cudaDMACustom, include/cudaDMA.h:4184-4208): only the handshake; the DMA
+ * threads fill the buffer with a copy loop of their own, ordinary loads and stores, between
+ * wait_for_dma_start() and finish_async_dma(). `iters` buffers of nfloats floats go through one
+ * shared buffer. PLAIN_WAIT selects wait_for_dma_start_for_stores(), the same wait without the
+ * fence that only asynchronous copies need. */
+template <bool PLAIN_WAIT>
+__global__ void custom_copy_kernel(const float *__restrict__ idata, float *__restrict__ odata, int nfloats, int iters,
+                                   int ncompute, int ndma) {
+  extern __shared__ float buffer[];
+  CudaDMACustom dma(2, ndma, ncompute, ncompute);
+  if (dma.owns_this_thread()) {
+    const int t = threadIdx.x - ncompute;
+    for (int it = 0; it < iters; ++it) {
+      if (PLAIN_WAIT) dma.wait_for_dma_start_for_stores();
+      else dma.wait_for_dma_start();
+      for (int i = t; i < nfloats; i += ndma) buffer[i] = idata[(size_t)it * nfloats + i];
+      dma.finish_async_dma();
+    }
+  } else {
+    for (int it = 0; it < iters; ++it) {
+      dma.start_async_dma();
+      dma.wait_for_dma_finish();
+      for (int i = threadIdx.x; i < nfloats; i += ncompute) odata[(size_t)it * nfloats + i] = buffer[i];
+    }
+  }
+}
+#endif
+
 extern "C" {
 
 #ifdef HAVE_STATUS
+/* h_in, h_out: iters * nfloats floats. Returns 0, a negative argument / CUDA code, or the status
+ * word of a wait that gave up. */
+long long ENTRY(custom_copy)(int plain_wait, int nfloats, int iters, int ncompute, int ndma, const float *h_in,
+                             float *h_out) {
+  if (!h_in || !h_out || nfloats <= 0 || nfloats > 12000 || iters <= 0 || ncompute <= 0 || (ncompute & 31) || ndma <= 0 ||
+      (ndma & 31) || ncompute + ndma > 1024)
+    return -1;
+  const size_t bytes = (size_t)nfloats * iters * sizeof(float);
+  float *d_in = nullptr, *d_out = nullptr;
+  cudaError_t e = cudaMalloc(&d_in, bytes);
+  if (e == cudaSuccess) e = cudaMalloc(&d_out, bytes);
+  if (e == cudaSuccess) e = cudaMemcpy(d_in, h_in, bytes, cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) e = cudaMemset(d_out, 0, bytes);
+  if (e == cudaSuccess) {
+    if (plain_wait) custom_copy_kernel<true><<<1, ncompute + ndma, nfloats * sizeof(float)>>>(d_in, d_out, nfloats, iters, ncompute, ndma);
+    else custom_copy_kernel<false><<<1, ncompute + ndma, nfloats * sizeof(float)>>>(d_in, d_out, nfloats, iters, ncompute, ndma);
+    e = cudaGetLastError();
+  }
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaMemcpy(h_out, d_out, bytes, cudaMemcpyDeviceToHost);
+  unsigned int w = 0;
+  if (e == cudaSuccess) e = cudadma_b200::read_status(&w, 0);
+  cudaFree(d_in);
+  cudaFree(d_out);
+  return e == cudaSuccess ? (long long)w : -2;
+}
+
 /* Runs starved_kernel; returns the status word it left (0 would mean the wait never gave up),
  * negative on a CUDA error. The context stays usable. */
 long long ENTRY(starved_wait)(void) {

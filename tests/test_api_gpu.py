@@ -255,3 +255,22 @@ def test_a_wait_that_cannot_be_satisfied_gives_up_with_a_status():
     w = lib.apitest_starved_wait()
     assert w == (0x80000000 | (3 << 8) | 1), hex(w)
     check_sequential(1, 1, 0, 0, 16, 0, 4096, 64)  # the context is intact and the status word was cleared
+
+
+@pytest.mark.parametrize("plain_wait", (0, 1))
+@pytest.mark.parametrize("nfloats,iters,ncompute,ndma", [(256, 1, 32, 32), (1000, 7, 128, 64), (4096, 40, 256, 128),
+                                                         (33, 200, 64, 32)])
+def test_custom_object_runs_a_hand_written_copy_loop(plain_wait, nfloats, iters, ncompute, ndma):
+    """CudaDMACustom (v1 cudaDMACustom, include/cudaDMA.h:4184-4208) gives the caller nothing but the
+    handshake: the DMA threads copy with a loop of their own between wait_for_dma_start() and
+    finish_async_dma(), buffer after buffer through one shared buffer. Every buffer must come out
+    as it went in; a handshake that let either side run ahead would mix iterations."""
+    import ctypes
+    lib = harness.ours().lib
+    lib.apitest_custom_copy.restype = ctypes.c_longlong
+    lib.apitest_custom_copy.argtypes = [ctypes.c_int] * 5 + [ctypes.c_void_p, ctypes.c_void_p]
+    src = oracle.fill_uniform(nfloats * iters, 0xCC + nfloats, -1.0, 1.0)
+    out = np.zeros_like(src)
+    r = lib.apitest_custom_copy(plain_wait, nfloats, iters, ncompute, ndma, src.ctypes.data, out.ctypes.data)
+    assert r == 0, hex(r)
+    assert np.array_equal(out.view(np.uint32), oracle.sequential(src).view(np.uint32))

@@ -127,3 +127,44 @@ def test_two_gpus_overlapped_host_run_is_the_plain_run(nz, steps, exchange, chun
         assert np.array_equal(plain.view(np.uint32), one[lo:hi].view(np.uint32)), "rank %d: plain host run" % rank
         assert np.array_equal(over.view(np.uint32), one[lo:hi].view(np.uint32)), "rank %d: overlapped host run" % rank
         assert np.array_equal(more.view(np.uint32), one_more[lo:hi].view(np.uint32)), "rank %d: next step" % rank
+
+
+@pytest.mark.parametrize("nz,steps", [(40, 4), (230, 3)])
+def test_two_gpus_driven_from_one_process(nz, steps):
+    """cudadma_stencil25_multi_*: one process, one slab and one stream per GPU, neighbours joined by
+    peer access. The library keeps what it knows per device, so the second GPU of the process works
+    like the first; the field equals the one-GPU field bit for bit."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two CUDA devices")
+    import cudadma_b200 as cd
+    from oracle import oracle
+    nx, ny = 128, 64
+    field = oracle.fill_uniform(nx * ny * nz, 0xC4, 0.0, 1.0)
+    m = cd.MultiStencil(2, nx, ny, nz)
+    try:
+        m.load(field)
+        m.run(steps)
+        got = np.full_like(field, np.nan)
+        m.store(got)
+    finally:
+        m.destroy()
+    a = torch.from_numpy(field).cuda()
+    one = cd.stencil25_run(a, torch.zeros_like(a), nx, ny, nz, steps).cpu().numpy()
+    assert np.array_equal(got.view(np.uint32), one.view(np.uint32))
+    # every other entry point on the second device of the same process
+    with torch.cuda.device(1):
+        a1 = torch.from_numpy(field).cuda()
+        one1 = cd.stencil25_run(a1, torch.zeros_like(a1), nx, ny, nz, steps).cpu().numpy()
+        src = torch.from_numpy(oracle.fill_uniform(16384 * 5 // 4, 0xC1, -1.0, 1.0)).cuda()
+        dst = torch.zeros_like(src)
+        cd.seq_copy(dst, src)
+        g = torch.from_numpy(oracle.fill_index(1280, 0xC3A, 4096)).cuda()
+        p = torch.from_numpy(oracle.permutation(1280, 0xC3B)).cuda()
+        table = torch.from_numpy(oracle.fill_uniform(4096 * 8, 0xC3, -1.0, 1.0)).cuda()
+        out = torch.zeros(1280 * 8, device="cuda")
+        cd.gather_scatter(out, table, g, p, 1280)
+        torch.cuda.synchronize()
+        assert cd.device_status() == 0
+        assert torch.equal(dst, src)
+        assert torch.equal(out.view(1280, 8)[p.long()], table.view(4096, 8)[g.long()])
+    assert np.array_equal(one1.view(np.uint32), one.view(np.uint32))

@@ -130,14 +130,15 @@ def test_gather_scatter_record_sizes(impl, record_bytes, n, table_records):
     assert not out[n * w:].any()
 
 
+@pytest.mark.parametrize("mode", [1, 2, 3])
 @pytest.mark.parametrize("n,table_records", [(128, 1000), (128 * 333, 1 << 16), (1 << 16, 1 << 20)])
-def test_gather_scatter_tma_gather4(n, table_records):
-    """The TMA row-gather form gives the same bytes."""
+def test_gather_scatter_tma_rows(n, table_records, mode):
+    """The TMA forms (row gathers, row scatters, both) give the same bytes."""
     table = oracle.fill_uniform(table_records * 8, 0xC3, -1.0, 1.0)
     gidx = oracle.fill_index(n, 0xC3A, table_records)
     sidx = oracle.permutation(n, 0xC3B)
     d_out = torch.zeros(n * 8 + 64, dtype=torch.float32, device="cuda")
-    cd.gather_scatter_tma(d_out, dev(table), table_records, dev(gidx), dev(sidx), n)
+    cd.gather_scatter_tma(d_out, n, dev(table), table_records, dev(gidx), dev(sidx), n, 32, mode)
     status_clean()
     out = d_out.cpu().numpy()
     exp = oracle.gather_scatter(np.zeros(n * 8, dtype=np.float32), table, gidx, sidx, 32)
@@ -262,6 +263,20 @@ def test_stencil_full_size_linearity_and_sample():
     a = dev(field)
     cd.stencil25_step(b, a, n, n, n, 0, 24)
     got = b.view(n, n, n)[:24].cpu().numpy()
+    assert rel_err(got, exp) <= STENCIL_TOL
+
+
+def test_stencil_full_job_against_the_double_precision_oracle():
+    """The benchmark's single-GPU stencil job whole: 512^3, 10 steps, every point of the final field
+    against the double-precision host reference (max |gpu - ref| / max |ref| <= 1e-5)."""
+    n, steps = 512, 10
+    field = oracle.fill_uniform(n * n * n, 0xC4, 0.0, 1.0)
+    a = cd.fill_uniform(torch.empty(n * n * n, dtype=torch.float32, device="cuda"), 0xC4, 0.0, 1.0)
+    assert torch.equal(a.view(torch.int32), dev(field).view(torch.int32)), "device and host generators agree"
+    b = torch.zeros_like(a)
+    got = cd.stencil25_run(a, b, n, n, n, steps).cpu().numpy().reshape(n, n, n)
+    status_clean()
+    exp = oracle.stencil25_f64(field.reshape(n, n, n), cd.STENCIL_COEFFS, steps)
     assert rel_err(got, exp) <= STENCIL_TOL
 
 
