@@ -278,6 +278,54 @@ def same_bits(dev_tensor, host_array):
     return bool(np.array_equal(got, np.ascontiguousarray(host_array).reshape(-1).view(np.uint32)))
 
 
+def pick_bpt(call, flush=None):
+    """The reference's classes take BYTES_PER_THREAD, their register staging budget, as a template
+    argument; the reference arm tries 64, 128 and 192 and keeps the fastest (median of 7 launches)."""
+    from oracle import reference as ref
+    times = {}
+    for bpt in ref.BPTS:
+        f = lambda: call(bpt)
+        f()
+        times[bpt], _ = median_launch_ms(f, 7, flush)
+    best = min(times, key=times.get)
+    return {"best": best, "ms": {str(k): round(v, 4) for k, v in times.items()}}
+
+
+REFERENCE_STENCIL_FORMS = ("windows_bpt64", "windows_bpt128", "windows_bpt192", "halo_ring")
+
+
+def reference_stencil_step(form):
+    """step(out, in, nx, ny, nz, z_begin, z_end, coeff) on padded arrays through the reference's classes:
+    whole windows by CudaDMAStrided (three staging budgets) or ring by v1 cudaDMAHalo + interior by cudaDMAStrided."""
+    from oracle import reference as ref
+    if form == "halo_ring":
+        return lambda o, i, nx, ny, nz, zb, ze, c: ref.halo_stencil25_step_padded(o, i, nx, ny, nz, zb, ze, c)
+    bpt = int(form.rsplit("bpt", 1)[1])
+    return lambda o, i, nx, ny, nz, zb, ze, c: ref.stencil25_step_padded(o, i, nx, ny, nz, zb, ze, c, 0, bpt)
+
+
+_REFERENCE_STENCIL = {}
+
+
+def pick_reference_stencil(a, b, nx, ny, nz):
+    """Times every form of the reference-class stencil on the given padded arrays and names the fastest."""
+    import cudadma_b200 as cd
+    from oracle import reference as ref
+    times = {}
+    for form in REFERENCE_STENCIL_FORMS:
+        if form == "halo_ring" and not ref.halo_stencil_available():
+            continue
+        step = reference_stencil_step(form)
+
+        def f():
+            step(b, a, nx, ny, nz, 0, nz, cd.STENCIL_COEFFS)
+        f()
+        times[form], _ = median_launch_ms(f, 5)
+    best = min(times, key=times.get)
+    _REFERENCE_STENCIL["best"] = best
+    return {"best": best, "ms_per_step": {k: round(v, 4) for k, v in times.items()}}
+
+
 def run_patterns(kind, peak):
     """Device-timed GB/s of the three data-movement patterns and the 512^3 stencil.
     kind: "native", "portable" (this repository) or "reference" (oracle/_ref).
@@ -297,14 +345,18 @@ def run_patterns(kind, peak):
     # sequential: 64 MiB, 16 KiB chunks
     n = 1 << 24
     src, dst = seeded_field(n, 0xC1, -1.0, 1.0), torch.zeros(n, device="cuda")
+    bpt_seq = None
     if kind == "reference":
-        f = lambda: ref.seq_copy(dst, src, n * 4)
+        bpt_seq = pick_bpt(lambda bpt: ref.seq_copy(dst, src, n * 4, bpt), flush)
+        f = lambda: ref.seq_copy(dst, src, n * 4, bpt_seq["best"])
     else:
         f = lambda: cd.seq_copy(dst, src, n * 4, 16384, kind)
     for _ in range(3):
         f()
     ms, best = median_launch_ms(f, 30, flush)
     res["sequential_64MiB"] = entry(ms, best, 2 * n * 4)
+    if bpt_seq:
+        res["sequential_64MiB"]["bytes_per_thread"] = bpt_seq
     res["sequential_64MiB"]["parity"] = "pass" if same_bits(dst, expected("sequential")) else "FAIL"
     # what a plain device-to-device copy of the same 64 MiB takes in the same loop (same L2 flush, same event
     # pair): the job lasts under 30 us, most of which is the ramp of an idle GPU, whatever kernel runs
@@ -322,7 +374,7 @@ def run_patterns(kind, peak):
     pairs = [(seeded_field(n, 0xC10 + i, -1.0, 1.0), torch.empty(n, device="cuda")) for i in range(12)]
     cur_stream = torch.cuda.current_stream().cuda_stream  # looked up once: the launches must not wait for Python
     if kind == "reference":
-        rot = lambda: [ref.seq_copy(d, s_, n * 4) for _ in range(2) for s_, d in pairs]
+        rot = lambda: [ref.seq_copy(d, s_, n * 4, bpt_seq["best"]) for _ in range(2) for s_, d in pairs]
     else:
         rot = lambda: [cd.seq_copy(d, s_, n * 4, 16384, kind, cur_stream) for _ in range(2) for s_, d in pairs]
     rot()
@@ -338,13 +390,16 @@ def run_patterns(kind, peak):
     nb = 1 << 28
     big_s, big_d = seeded_field(nb, 0xC1, -1.0, 1.0), torch.empty(nb, device="cuda")
     if kind == "reference":
-        f = lambda: ref.seq_copy(big_d, big_s, nb * 4)
+        bpt_big = pick_bpt(lambda bpt: ref.seq_copy(big_d, big_s, nb * 4, bpt))
+        f = lambda: ref.seq_copy(big_d, big_s, nb * 4, bpt_big["best"])
     else:
         f = lambda: cd.seq_copy(big_d, big_s, nb * 4, 16384, kind)
     for _ in range(3):
         f()
     ms, best = median_launch_ms(f, 10)
     res["sequential_1GiB"] = entry(ms, best, 2 * nb * 4)
+    if kind == "reference":
+        res["sequential_1GiB"]["bytes_per_thread"] = bpt_big
     ok = torch.equal(big_d.view(torch.int32), big_s.view(torch.int32))
     res["sequential_1GiB"]["parity"] = "pass" if ok else "FAIL"
     g = lambda: big_d.copy_(big_s)
@@ -358,13 +413,16 @@ def run_patterns(kind, peak):
     m = 16384
     a, b = seeded_field(m * m, 0xC2, -1.0, 1.0), torch.zeros(m * m, device="cuda")
     if kind == "reference":
-        f = lambda: ref.strided_transpose(b, a, m, m)
+        bpt_tr = pick_bpt(lambda bpt: ref.strided_transpose(b, a, m, m, bpt))
+        f = lambda: ref.strided_transpose(b, a, m, m, bpt_tr["best"])
     else:
         f = lambda: cd.strided_transpose(b, a, m, m, kind)
     for _ in range(3):
         f()
     ms, best = median_launch_ms(f, 10)
     res["strided_16384"] = entry(ms, best, 2 * m * m * 4)
+    if kind == "reference":
+        res["strided_16384"]["bytes_per_thread"] = bpt_tr
     res["strided_16384"]["parity"] = "pass" if same_bits(b, expected("strided")) else "FAIL"
     del a, b
 
@@ -376,13 +434,16 @@ def run_patterns(kind, peak):
     si = torch.from_numpy(perm).cuda()
     out = torch.zeros(n * 8, device="cuda")
     if kind == "reference":
-        f = lambda: ref.gather_scatter(out, table, gi, si, n)
+        bpt_gs = pick_bpt(lambda bpt: ref.gather_scatter(out, table, gi, si, n, bpt), flush)
+        f = lambda: ref.gather_scatter(out, table, gi, si, n, bpt_gs["best"])
     else:
         f = lambda: cd.gather_scatter(out, table, gi, si, n, 32, kind)
     for _ in range(3):
         f()
     ms, best = median_launch_ms(f, 20, flush)
     res["indirect_2e22x32B"] = entry(ms, best, n * 72)
+    if kind == "reference":
+        res["indirect_2e22x32B"]["bytes_per_thread"] = bpt_gs
     res["indirect_2e22x32B"]["payload_gbs"] = round(n * 64 / ms / 1e6, 1)
     res["indirect_2e22x32B"]["parity"] = "pass" if same_bits(out, want) else "FAIL"
     del out
@@ -413,8 +474,12 @@ def run_patterns(kind, peak):
         pad = (nx + 8) * (ny + 8) * (nz + 8)
         a, b = torch.zeros(pad, device="cuda"), torch.zeros(pad, device="cuda")
         a.view(nz + 8, ny + 8, nx + 8)[4:-4, 4:-4, 4:-4] = seeded_field(pts, 0xC4).view(nz, ny, nx)
-        step = ref.stencil25_step_padded if kind == "reference" else cd.stencil25_step_padded
         coeff = cd.STENCIL_COEFFS
+        if kind == "reference":
+            choice = pick_reference_stencil(a, b, nx, ny, nz)
+            step = reference_stencil_step(choice["best"])
+        else:
+            step = cd.stencil25_step_padded
 
         def f():
             x, y = a, b
@@ -425,10 +490,60 @@ def run_patterns(kind, peak):
     ms, best = median_launch_ms(f, 5)
     res["stencil_512"] = entry(ms / 10, best / 10, pts * BYTES_PER_POINT)
     res["stencil_512"]["gpts"] = round(pts * 10 / ms / 1e6, 1)
+    if kind == "reference":
+        res["stencil_512"]["form"] = choice
     del a, b
     if kind != "reference":
         res["device_status"] = cd.device_status()
     return res
+
+
+def run_examples():
+    """The reference's own kernels on both headers (oracle/_ref, built from the reference checkout): its five
+    stencil buffering examples on their default problem, its two saxpy example pairs and its throughput
+    benchmark, each compiled unmodified against the reference header and against this repository's.
+    `ratio` = reference-header time / this-header time (above 1: this header is faster)."""
+    import numpy as np
+    from oracle import examples as ex, oracle
+    out = {}
+    if ex.available("libexamples_ours.so", "libexamples_ref.so"):
+        dims = ex.STENCIL_DEFAULT_DIMS
+        shape = (dims[2] + 8, dims[1] + 8, dims[0] + 8, 2)
+        src = oracle.fill_uniform(int(np.prod(shape)), 0xE0, -1.0, 1.0).reshape(shape)
+        for kid, name in enumerate(ex.STENCIL_NAMES):
+            t = {}
+            for which in ("ours", "ref", "ours", "ref"):   # interleaved, best of two
+                _, ms = ex.run_stencil(which, kid, src, dims)
+                t[which] = min(ms, t.get(which, ms))
+            out["stencil_" + name] = {"this_header_ms": round(t["ours"], 4), "reference_header_ms": round(t["ref"], 4),
+                                      "ratio": round(t["ref"] / t["ours"], 3),
+                                      "this_header_gbs": round(ex.stencil_bandwidth_gbs(dims, t["ours"]), 1),
+                                      "reference_header_gbs": round(ex.stencil_bandwidth_gbs(dims, t["ref"]), 1)}
+    for example in ("sequential", "strided"):
+        tag = "strided_" if example == "strided" else ""
+        if not ex.available("libv1saxpy_%sours.so" % tag, "libv1saxpy_%sref.so" % tag):
+            continue
+        n = ex.saxpy_elements(example)
+        x, y = oracle.fill_uniform(n, 0x5A0, 0.0, 1.0), oracle.fill_uniform(n, 0x5B0, 0.0, 1.0)
+        for kernel_id, kname in enumerate(("saxpy_cudaDMA", "saxpy_cudaDMA_doublebuffer")):
+            t = {}
+            for which in ("ours", "ref", "ours", "ref"):
+                _, ms = ex.run_saxpy(example, which, kernel_id, x, y, 0.84018773)
+                t[which] = min(ms, t.get(which, ms))
+            out["%s_%s" % (kname, example)] = {"this_header_ms": round(t["ours"], 4), "reference_header_ms": round(t["ref"], 4),
+                                                "ratio": round(t["ref"] / t["ours"], 3)}
+    if ex.available("libperfseq_ours.so", "libperfseq_ref.so"):
+        for kid, name in enumerate(ex.PERFSEQ_NAMES):
+            g = {}
+            for which in ("ours", "ref", "ours", "ref"):
+                gbs, _ = ex.run_perf_sequential(which, kid)
+                g[which] = max(gbs, g.get(which, gbs))
+            out["perf_sequential_" + name] = {"this_header_gbs": round(g["ours"], 1), "reference_header_gbs": round(g["ref"], 1),
+                                              "ratio": round(g["ours"] / g["ref"], 3)}
+    if not out:
+        return {"unavailable": "oracle/_ref holds no example libraries (no reference checkout at build time)"}
+    out["slowest_ratio"] = min(v["ratio"] for v in out.values())
+    return out
 
 
 # ------------------------------------------------------------------ the stencil job
@@ -462,11 +577,18 @@ def make_stencil(impl, nz_global, weights=None):
     from cudadma_b200.sharded import ShardedStencil
     if impl == "ours":
         return ShardedStencil(NX, NY, nz_global, exchange=EXCHANGE, weights=weights)
-    from oracle import reference as ref
+    if "best" not in _REFERENCE_STENCIL:
+        # which form of the reference-class stencil is fastest here: tried once, on a 1024 x 1024 x 64 padded slab
+        pad = (NX + 8) * (NY + 8) * (64 + 8)
+        pa, pb = torch.zeros(pad, device="cuda"), torch.zeros(pad, device="cuda")
+        pa.view(72, NY + 8, NX + 8)[4:-4, 4:-4, 4:-4] = seeded_field(NX * NY * 64, 0xC4).view(64, NY, NX)
+        _REFERENCE_STENCIL["choice"] = pick_reference_stencil(pa, pb, NX, NY, 64)
+        del pa, pb
+    ref_step = reference_stencil_step(_REFERENCE_STENCIL["best"])
 
     def step(out, inp, nx, ny, nz_total, zb, ze, coeff):
         # padded layout: the four ghost planes of a slab are the z border of the padded array
-        ref.stencil25_step_padded(out, inp, nx, ny, nz_total - 8, zb - 4, ze - 4, coeff)
+        ref_step(out, inp, nx, ny, nz_total - 8, zb - 4, ze - 4, coeff)
     return ShardedStencil(NX, NY, nz_global, step_fn=step, pad_xy=4, device=torch.device("cuda", torch.cuda.current_device()))
 
 
@@ -566,6 +688,25 @@ def run_stencil_job(impl, args, rank, world, local, peak, peak_kind):
     status = cd.device_status() if impl == "ours" else 0
     sm_mhz = probe.mhz()
     parity = sharded_parity(st, world) if impl == "ours" else None
+
+    # the same job with this repository's kernel but the exchange the reference arm has to use (NCCL send/recv of the
+    # boundary planes): against the reference arm's figure it isolates the kernel, against `value` the exchange
+    nccl_form = None
+    if impl == "ours" and world > 1 and EXCHANGE == "p2p":
+        from cudadma_b200.sharded import ShardedStencil
+        del st
+        torch.cuda.empty_cache()
+        stn = ShardedStencil(NX, NY, NZ, exchange="nccl", weights=rates)
+        stn.load(slab_of_global_field(stn))
+        for _ in range(3):
+            stn.step()
+        msn = time_region(stn.step, args.steps)
+        nccl_form = {"value": round(NX * NY * NZ * args.steps / msn / 1e6, 2), "unit": "Gpts/s",
+                     "ms_per_step": round(msn / args.steps, 4),
+                     "note": "boundary planes first, torch.distributed send/recv on a side stream, interior meanwhile"}
+        del stn
+        torch.cuda.empty_cache()
+        st = make_stencil(impl, NZ, rates)
 
     # weak-scaling companion: 256 planes per GPU (the 8-GPU point is the configuration above)
     weak = None
@@ -667,6 +808,8 @@ def run_stencil_job(impl, args, rank, world, local, peak, peak_kind):
         line["parity_detail"] = parity
     if weak is not None:
         line["weak"] = weak
+    if nccl_form is not None:
+        line["nccl_exchange"] = nccl_form
     return line, st
 
 
@@ -796,11 +939,14 @@ def main():
         line["launches_total_this_process"] = cd.launch_count() - before
     else:
         line["impl"] = "reference"
-        line["config"]["reference_build"] = ("reference CudaDMA classes (cudaDMAv2.h) compiled for sm_100a, "
-                                             "CudaDMAStrided window loads from zero-padded arrays")
+        line["config"]["reference_build"] = ("reference CudaDMA classes compiled for sm_100a on zero-padded arrays; the fastest of: "
+                                             "whole windows by CudaDMAStrided (cudaDMAv2.h) with BYTES_PER_THREAD 64 / 128 / 192, "
+                                             "ring by v1 cudaDMAHalo + interior by cudaDMAStrided (cudaDMA.h)")
+        line["config"]["reference_stencil_form"] = _REFERENCE_STENCIL.get("choice", _REFERENCE_STENCIL.get("best"))
     if rank == 0 and world == 1 and not args.no_patterns:
         if impl == "ours":
             line["patterns"] = {"native": run_patterns("native", peak), "portable": run_patterns("portable", peak)}
+            line["patterns"]["examples"] = run_examples()
         else:
             line["patterns"] = {"reference": run_patterns("reference", peak)}
     if rank == 0 and not args.no_cpu and (world == 1 or impl == "reference"):

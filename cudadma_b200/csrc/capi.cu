@@ -26,26 +26,33 @@
 #ifndef SEQ_BULK_STORE
 #define SEQ_BULK_STORE true
 #endif
+
 #ifndef TR_STAGES
 #define TR_STAGES 3
 #endif
 #ifndef TR_CTAS_PER_SM
 #define TR_CTAS_PER_SM 2
 #endif
+#ifndef TR_SUPER
+#define TR_SUPER 2 /* tile numbering of the transpose, see dma_kernels.cuh: 2 measured 0.8 % over 1, 4 to 16 below it */
+#endif
 #ifndef HOST_PIPE_CHUNK_BYTES
 #define HOST_PIPE_CHUNK_BYTES ((size_t)128 << 20) /* piece of the field per upload in the overlapped host run */
 #endif
 #ifndef GS_STAGES
-#define GS_STAGES 8
+#define GS_STAGES 4 /* buffers per CTA and direction; 8 measured 2 % slower at the same number of CTAs */
 #endif
 #ifndef GS_CTAS_PER_SM
-#define GS_CTAS_PER_SM 4
+#define GS_CTAS_PER_SM 8 /* upper bound; the launch takes what is resident (five per SM at 40 registers) */
 #endif
 #ifndef STENCIL25_L2PROMO
 #define STENCIL25_L2PROMO CU_TENSOR_MAP_L2_PROMOTION_L2_256B
 #endif
 #ifndef STENCIL_CTAS_TARGET
 #define STENCIL_CTAS_TARGET 8 /* CTAs per SM the automatic z_chunk aims for (two are resident) */
+#endif
+#ifndef STENCIL_MAX_RUN
+#define STENCIL_MAX_RUN 128 /* longest run of planes the automatic z_chunk gives one CTA (see plan_chunks) */
 #endif
 
 #include "cudadma.h"
@@ -236,10 +243,16 @@ ChunkPlan plan_chunks(int depth, long long tiles, int sms, int z_chunk, int z_ed
   if (z_edge > 0 && depth < 2 * z_edge + 1) z_edge = 0;
   const int inner = depth - 2 * z_edge;
   if (z_chunk <= 0) {
-    /* enough CTAs for a few waves over the SMs, but runs of at least 32 planes so that the
-     * eight lead-in/lead-out planes of a run stay a small share of its loads */
+    /* Enough CTAs for a few waves over the SMs, but runs of at least 32 planes so that the eight
+     * lead-in/lead-out planes of a run stay a small share of its loads -- and of at most
+     * STENCIL_MAX_RUN planes: the CTAs of a wave start on the same plane and read each other's
+     * halo cells out of L2, but over a long run they drift apart in z until those cells come from
+     * DRAM a second time. On a rested GPU, 1024 x 1024 x 2048: 747 Gpts/s with runs of 128 planes,
+     * 721 with 64, 625 with 256, 585 with 512 or 1024. */
     const long long want = (long long)STENCIL_CTAS_TARGET * sms - (z_edge > 0 ? 2 * tiles : 0);
     long long chunks = (want + tiles - 1) / tiles;
+    const long long least = ((long long)inner + STENCIL_MAX_RUN - 1) / STENCIL_MAX_RUN;
+    if (chunks < least) chunks = least;
     if (chunks < 1) chunks = 1;
     z_chunk = (int)((inner + chunks - 1) / chunks);
     if (z_chunk < 32) z_chunk = 32;
@@ -623,12 +636,12 @@ int cudadma_gather_scatter(void *out, const void *table, const int32_t *gather_i
   char *o = static_cast<char *>(out);
   const char *t = static_cast<const char *>(table);
   if (impl == CUDADMA_IMPL_NATIVE) {
-    /* ring depth: GS_STAGES buffers while a buffer is at most 8 KiB, half of that for 16 KiB buffers */
+    /* ring depth: GS_STAGES buffers while a buffer is at most 8 KiB, half of that (at least two) for 16 KiB buffers */
     switch (record_bytes) {
       case 16: return launch_gather_scatter<16, GS_STAGES>(o, t, gather_idx, scatter_idx, nbuf, GS_CTAS_PER_SM, sms, s);
       case 32: return launch_gather_scatter<32, GS_STAGES>(o, t, gather_idx, scatter_idx, nbuf, GS_CTAS_PER_SM, sms, s);
       case 64: return launch_gather_scatter<64, GS_STAGES>(o, t, gather_idx, scatter_idx, nbuf, GS_CTAS_PER_SM, sms, s);
-      default: return launch_gather_scatter<128, GS_STAGES / 2>(o, t, gather_idx, scatter_idx, nbuf, GS_CTAS_PER_SM, sms, s);
+      default: return launch_gather_scatter<128, (GS_STAGES / 2 < 2 ? 2 : GS_STAGES / 2)>(o, t, gather_idx, scatter_idx, nbuf, GS_CTAS_PER_SM, sms, s);
     }
   }
   int r;

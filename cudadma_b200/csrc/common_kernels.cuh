@@ -71,14 +71,19 @@ __device__ __forceinline__ void bridge_gather_to_scatter(GRING &g, SRING &sc, co
 constexpr int GS_GATHER_THREADS = 128, GS_SCATTER_THREADS = 128, GS_BRIDGE_THREADS = 32;
 constexpr int GS_THREADS = GS_BRIDGE_THREADS + GS_GATHER_THREADS + GS_SCATTER_THREADS;
 
-template <int RECORD_BYTES, int RECORDS, int STAGES>
-__global__ void __launch_bounds__(GS_THREADS)
+#ifndef GS_MIN_BLOCKS
+#define GS_MIN_BLOCKS 7 /* seven CTAs of 288 threads fill an SM's 2048 thread slots: at most 32 registers. The kernel
+                           is bound by how many records are in flight, and 40 registers (five CTAs) cost it 9 % */
+#endif
+/* BPT: the BYTES_PER_THREAD template argument of the objects (the reference's register staging budget) */
+template <int RECORD_BYTES, int RECORDS, int STAGES, int BPT = 64>
+__global__ void __launch_bounds__(GS_THREADS, GS_MIN_BLOCKS)
 gather_scatter_kernel(char *__restrict__ out, const char *__restrict__ table, const int *__restrict__ gather_idx,
                       const int *__restrict__ scatter_idx, const long long nbuffers) {
   extern __shared__ __align__(128) unsigned char smem[];
   constexpr int BUF = RECORD_BYTES * RECORDS;
-  typedef CudaDMAIndirect<true, true, 16, 64, RECORD_BYTES, GS_GATHER_THREADS, RECORDS> Gather;
-  typedef CudaDMAIndirect<false, true, 16, 64, RECORD_BYTES, GS_SCATTER_THREADS, RECORDS> Scatter;
+  typedef CudaDMAIndirect<true, true, 16, BPT, RECORD_BYTES, GS_GATHER_THREADS, RECORDS> Gather;
+  typedef CudaDMAIndirect<false, true, 16, BPT, RECORD_BYTES, GS_SCATTER_THREADS, RECORDS> Scatter;
   Ring<Gather, STAGES, 0> g(GS_BRIDGE_THREADS, GS_BRIDGE_THREADS);
   Ring<Scatter, STAGES, STAGES> sc(GS_BRIDGE_THREADS, GS_BRIDGE_THREADS + GS_GATHER_THREADS);
   const long long stride = gridDim.x;

@@ -12,6 +12,8 @@
 
 #include <cuda_runtime.h>
 
+#include "portable_stencil_math.cuh"
+
 namespace portable {
 
 constexpr int P_DMA = 128, P_COMPUTE = 256, P_CHUNK = 16384;
@@ -128,22 +130,7 @@ transpose_kernel(float *__restrict__ out, const float *__restrict__ in, const in
  * a per-thread register queue that each thread refills from global memory.
  * Padded layout: grid cell (x, y, z) is element ((z + 4) * py + (y + 4)) * px + (x + 4), px = nx + 8,
  * py = ny + 8, all border cells zero. Needs nx % 32 == 0 and ny % 16 == 0. */
-constexpr int PS_TX = 32, PS_TY = 16, PS_R = 4, PS_WX = PS_TX + 2 * PS_R, PS_WY = PS_TY + 2 * PS_R;
-constexpr int PS_COMPUTE = PS_TX * PS_TY, PS_DMA = 64;
-struct PCoeffs { float c[5]; };
-
-__device__ __forceinline__ float stencil_point(const float *__restrict__ w, const float cur, const float (&b)[4],
-                                               const float (&f)[4], const PCoeffs &k) {
-  /* w points at this thread's cell inside the 40 x 24 window */
-  float acc = k.c[0] * cur;
-#pragma unroll
-  for (int r = 1; r <= PS_R; ++r) {
-    const float s = ((w[-r] + w[r]) + (w[-r * PS_WX] + w[r * PS_WX])) + (b[r - 1] + f[r - 1]);
-    acc = fmaf(k.c[r], s, acc);
-  }
-  return acc;
-}
-
+/* tile shape, coefficients and the per-point arithmetic: portable_stencil_math.cuh */
 template <int BPT>
 __global__ void __launch_bounds__(PS_COMPUTE + PS_DMA)
 stencil_kernel(float *__restrict__ out, const float *__restrict__ in, const int px, const int py, const int z_begin,
@@ -200,16 +187,18 @@ stencil_kernel(float *__restrict__ out, const float *__restrict__ in, const int 
 
 /* ---- launchers: return a cudaError_t as int (0 = launched) ---- */
 
+template <int BPT = 64>
 inline int launch_seq_copy(char *dst, const char *src, long long nchunks, int sms, cudaStream_t s) {
-  auto k = seq_copy_kernel<64>;
+  auto k = seq_copy_kernel<BPT>;
   const long long want = 4ll * sms; /* 32 KiB of shared memory and 384 threads per CTA */
   const int grid = (int)(nchunks < want ? nchunks : want);
   k<<<grid, P_DMA + P_COMPUTE, 2 * P_CHUNK, s>>>(dst, src, nchunks);
   return (int)cudaGetLastError();
 }
 
+template <int BPT = 64>
 inline int launch_transpose(float *dst, const float *src, int rows, int cols, int sms, cudaStream_t s) {
-  auto k = transpose_kernel<64>;
+  auto k = transpose_kernel<BPT>;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * PT_BUF);
   if (e != cudaSuccess) return (int)e;
   const long long ntiles = (long long)(rows / PT_ROWS) * (cols / PT_COLS);
@@ -219,24 +208,31 @@ inline int launch_transpose(float *dst, const float *src, int rows, int cols, in
   return (int)cudaGetLastError();
 }
 
-template <int RECORD_BYTES = 32>
+template <int RECORD_BYTES = 32, int BPT = 64>
 inline int launch_gather_scatter(char *out, const char *table, const int *gidx, const int *sidx, long long nbuf,
                                  int sms, cudaStream_t s) {
   using namespace cudadma_b200::kernels;
   constexpr int STAGES = 4; /* dmaIDs 0..3 gather, 4..7 scatter: all sixteen named barriers of the reference */
   constexpr int SMEM = STAGES * 128 * RECORD_BYTES;
-  auto k = gather_scatter_kernel<RECORD_BYTES, 128, STAGES>;
+  auto k = gather_scatter_kernel<RECORD_BYTES, 128, STAGES, BPT>;
   if (SMEM > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return (int)e;
   }
-  const long long want = (SMEM <= 32 * 1024 ? 6ll : 3ll) * sms;
+  /* one resident wave: a CTA keeps its share of the buffers to itself, so CTAs that only start
+   * when others have finished would run the tail of the job at a fraction of the occupancy */
+  int fit = 0;
+  cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&fit, k, GS_THREADS, SMEM);
+  if (e != cudaSuccess) return (int)e;
+  if (fit < 1) fit = 1;
+  const long long want = (long long)fit * sms;
   const int grid = (int)(nbuf < want ? nbuf : want);
   k<<<grid, GS_THREADS, SMEM, s>>>(out, table, gidx, sidx, nbuf);
   return (int)cudaGetLastError();
 }
 
 /* padded arrays (see stencil_kernel); output planes [z_begin, z_end) of the nx x ny x nz grid */
+template <int BPT = 64>
 inline int launch_stencil_padded(float *out, const float *in, int nx, int ny, int nz, int z_begin, int z_end,
                                  const float coeff[5], int z_chunk, int sms, cudaStream_t s) {
   if (nx % PS_TX || ny % PS_TY || z_begin < 0 || z_end > nz || z_begin >= z_end) return (int)cudaErrorInvalidValue;
@@ -253,7 +249,7 @@ inline int launch_stencil_padded(float *out, const float *in, int nx, int ny, in
     if (z_chunk > depth) z_chunk = depth;
   }
   dim3 grid(nx / PS_TX, ny / PS_TY, (depth + z_chunk - 1) / z_chunk);
-  stencil_kernel<64><<<grid, PS_COMPUTE + PS_DMA, 0, s>>>(out, in, nx + 2 * PS_R, ny + 2 * PS_R, z_begin, z_end,
+  stencil_kernel<BPT><<<grid, PS_COMPUTE + PS_DMA, 0, s>>>(out, in, nx + 2 * PS_R, ny + 2 * PS_R, z_begin, z_end,
                                                           z_chunk, k);
   return (int)cudaGetLastError();
 }

@@ -239,10 +239,10 @@ __device__ __forceinline__ void compute_side(RING &ring, const unsigned char *sm
     }
     if (sync.ticket) {
       /* This CTA is done with the ghost planes and with its stores into the neighbours. All its
-       * compute threads meet at a hardware barrier (id 1; the objects use mbarriers); thread 0 then
+       * compute threads meet at a hardware barrier (id 15, which no object uses); thread 0 then
        * makes their stores visible system-wide (the fence is cumulative over what the barrier
        * ordered before it) and takes a ticket; the last boundary CTA of the launch publishes. */
-      asm volatile("bar.sync 1, %0;" ::"n"(COMPUTE_THREADS) : "memory");
+      asm volatile("bar.sync 15, %0;" ::"n"(COMPUTE_THREADS) : "memory");
       if (threadIdx.x == 0) {
         __threadfence_system();
         const unsigned int t = atomicAdd(sync.ticket, 1u);

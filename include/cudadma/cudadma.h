@@ -32,7 +32,7 @@
 #include <stdio.h>
 
 #ifndef CUDADMA_MAX_IDS
-#define CUDADMA_MAX_IDS 16 /* dmaID range per CTA: 0 .. CUDADMA_MAX_IDS-1 */
+#define CUDADMA_MAX_IDS 16 /* dmaID range per CTA: 0 .. CUDADMA_MAX_IDS-1 (a power of two) */
 #endif
 #ifndef CUDADMA_WAIT_LIMIT_CYCLES
 #define CUDADMA_WAIT_LIMIT_CYCLES (1ll << 31) /* about one second of SM clocks */
@@ -204,6 +204,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+/* hardware (named) barriers: id 1..15, count a multiple of 32 */
+__device__ __forceinline__ void named_sync(uint32_t id, uint32_t count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+__device__ __forceinline__ void named_arrive(uint32_t id, uint32_t count) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
 __device__ __forceinline__ void fence_proxy_async() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
@@ -309,7 +316,9 @@ namespace detail {
 /* Two mbarriers per dmaID, shared by every object of the CTA. */
 __device__ __forceinline__ uint32_t barrier_addr(int dmaID, int which) {
   __shared__ __align__(8) unsigned long long bars[2 * CUDADMA_MAX_IDS];
-  return ptx::smem_u32(bars) + 8u * (2u * (unsigned)dmaID + (unsigned)which);
+  /* an id outside 0 .. CUDADMA_MAX_IDS - 1 wraps around (and the constructor records a status code)
+   * rather than addressing shared memory that belongs to somebody else */
+  return ptx::smem_u32(bars) + 8u * (2u * ((unsigned)dmaID % (unsigned)CUDADMA_MAX_IDS) + (unsigned)which);
 }
 
 /* Slow half of a wait: keeps polling, gives up after CUDADMA_WAIT_LIMIT_CYCLES
@@ -427,18 +436,42 @@ __device__ __forceinline__ unsigned long long addr_bits(const void *p) {
 /* ------------------------------------------------------------------------- */
 class CudaDMA {
  public:
-  /* do_sync == false builds an object without barriers (non-specialised mode). */
+  /* do_sync == false builds an object without barriers (non-specialised mode).
+   * async_proxy == false: the derived class knows at compile time that none of its transfers can go
+   * through the bulk-copy engine (rows too short for it), so the two calls that hand the buffer
+   * over need no proxy fence; the tensor-map extensions of such a class fence for themselves.
+   * hardware_barriers == true: the derived class never issues an asynchronous copy at all (it
+   * moves its bytes through registers, or the caller does), so nothing has to be counted by an
+   * mbarrier and the handshake can be the reference's own pair of hardware barriers
+   * (bar.sync / bar.arrive, cudaDMAv2.h:65-75), whose crossing is cheaper (about 50 ns against 80).
+   * Barrier ids are 2 * dmaID + 1 (empty) and 2 * dmaID + 2 (full), so id 0 (__syncthreads) stays
+   * free and dmaIDs 0..6 qualify (which object does is decided by its type and its dmaID alone,
+   * so with a literal dmaID the other mechanism costs no registers); objects with a higher dmaID
+   * use mbarriers as all others do. As in the reference, the DMA threads and the compute threads
+   * of such an object must each be whole warps (bar counts threads in units of 32), and a wait on
+   * a hardware barrier is NOT bounded: it hangs when the two sides disagree about the thread
+   * counts. -DCUDADMA_NO_NAMED_BARRIERS keeps every object on mbarriers and every wait bounded. */
   __device__ __forceinline__ CudaDMA(const int dmaID, const int num_dma_threads, const int num_compute_threads,
-                                     const int dma_threadIdx_start, const bool do_sync = true)
+                                     const int dma_threadIdx_start, const bool do_sync = true,
+                                     const bool async_proxy = true, const bool hardware_barriers = false)
       : m_dma_tid(int(threadIdx.x) - dma_threadIdx_start),
         m_num_dma_threads(num_dma_threads),
         m_is_dma_thread((int(threadIdx.x) >= dma_threadIdx_start) &&
                         (int(threadIdx.x) < (dma_threadIdx_start + num_dma_threads))),
-        m_bar_empty(do_sync ? cudadma_b200::detail::barrier_addr(dmaID, 0) : 0u),
-        m_bar_full(do_sync ? cudadma_b200::detail::barrier_addr(dmaID, 1) : 0u),
+#ifdef CUDADMA_NO_NAMED_BARRIERS
+        m_named(false),
+#else
+        m_named(do_sync && hardware_barriers && dmaID >= 0 && dmaID <= 6),
+#endif
+        m_bar_empty(!do_sync ? 0u : m_named ? (uint32_t)(2 * dmaID + 1) : cudadma_b200::detail::barrier_addr(dmaID, 0)),
+        m_bar_full(!do_sync ? 0u : m_named ? (uint32_t)(2 * dmaID + 2) : cudadma_b200::detail::barrier_addr(dmaID, 1)),
         m_code(0x80000000u | ((unsigned)dmaID << 8)),
+        m_async_proxy(async_proxy),
+        m_count((uint32_t)(num_dma_threads + num_compute_threads)),
         m_phase(0) {
-    if (do_sync) {
+    if (do_sync && (dmaID < 0 || dmaID >= CUDADMA_MAX_IDS)) /* barrier_addr() wraps the id around; say so */
+      atomicCAS(&cudadma_b200::g_status_word, 0u, 0x8000D000u | ((unsigned)dmaID & 0xFFu));
+    if (do_sync && !m_named) {
       if (int(threadIdx.x) == dma_threadIdx_start) {
         cudadma_b200::ptx::mbar_init(m_bar_empty, (uint32_t)num_compute_threads);
         cudadma_b200::ptx::mbar_init(m_bar_full, (uint32_t)num_dma_threads);
@@ -451,7 +484,8 @@ class CudaDMA {
  public:
   /* compute threads: the buffer may be overwritten (or, for a scatter, read) by the DMA threads */
   __device__ __forceinline__ void start_async_dma(void) const {
-    cudadma_b200::ptx::fence_proxy_async();
+    if (m_named) { cudadma_b200::ptx::named_arrive(m_bar_empty, m_count); return; }
+    if (m_async_proxy) cudadma_b200::ptx::fence_proxy_async();
     cudadma_b200::ptx::mbar_arrive_warp(m_bar_empty);
   }
   /* Extension (not in the reference): start_async_dma() for compute threads that have only READ the
@@ -459,35 +493,45 @@ class CudaDMA {
    * WRITES visible to the bulk-copy engine; reads are ordered before the next transfer by the arrival
    * alone, so a kernel that releases a buffer every few hundred instructions can leave the fence out. */
   __device__ __forceinline__ void start_async_dma_after_reads(void) const {
+    if (m_named) { cudadma_b200::ptx::named_arrive(m_bar_empty, m_count); return; }
     cudadma_b200::ptx::mbar_arrive_warp(m_bar_empty);
   }
   /* compute threads: block until the transfer has landed */
   __device__ __forceinline__ void wait_for_dma_finish(void) const {
+    if (m_named) { cudadma_b200::ptx::named_sync(m_bar_full, m_count); return; }
     cudadma_b200::detail::bounded_wait(m_bar_full, m_phase, m_code | 2u);
     m_phase ^= 1u;
   }
   __device__ __forceinline__ bool owns_this_thread(void) const { return m_is_dma_thread; }
   /* DMA threads: block until the compute threads have released the buffer */
   __device__ __forceinline__ void wait_for_dma_start(void) const {
+    if (m_named) { cudadma_b200::ptx::named_sync(m_bar_empty, m_count); return; }
     cudadma_b200::detail::bounded_wait(m_bar_empty, m_phase, m_code | 1u);
     m_phase ^= 1u;
-    cudadma_b200::ptx::fence_proxy_async();
+    if (m_async_proxy) cudadma_b200::ptx::fence_proxy_async();
   }
   /* the same wait for DMA threads that will fill the buffer with ordinary stores: no proxy fence */
   __device__ __forceinline__ void wait_for_dma_start_for_stores(void) const {
+    if (m_named) { cudadma_b200::ptx::named_sync(m_bar_empty, m_count); return; }
     cudadma_b200::detail::bounded_wait(m_bar_empty, m_phase, m_code | 1u);
     m_phase ^= 1u;
   }
   /* DMA threads: this thread's share of the transfer is complete (or tracked by the barrier) */
-  __device__ __forceinline__ void finish_async_dma(void) const { cudadma_b200::ptx::mbar_arrive_warp(m_bar_full); }
+  __device__ __forceinline__ void finish_async_dma(void) const {
+    if (m_named) { cudadma_b200::ptx::named_arrive(m_bar_full, m_count); return; }
+    cudadma_b200::ptx::mbar_arrive_warp(m_bar_full);
+  }
 
  protected:
   const int m_dma_tid;
   const int m_num_dma_threads;
   const bool m_is_dma_thread;
-  const uint32_t m_bar_empty;
+  const bool m_named;         /* hardware barriers instead of mbarriers (see the constructor) */
+  const uint32_t m_bar_empty; /* shared-memory address of the mbarrier, or the hardware barrier's id */
   const uint32_t m_bar_full;
   const unsigned int m_code;
+  const bool m_async_proxy;
+  const uint32_t m_count;     /* threads of both sides together */
   mutable uint32_t m_phase; /* parity this thread waits for next (empty for DMA threads, full for compute) */
 };
 
@@ -639,6 +683,57 @@ __device__ __forceinline__ void prefetch_small(const char *src, const int rows, 
   for (int r = tid; r < rows; r += nthreads) ptx::bulk_prefetch_l2(src + (long long)r * src_stride, (uint32_t)row_bytes);
 }
 
+/*
+ * Register staging for small, fully templated transfers: ROWS rows of ROW_BYTES bytes (a multiple
+ * of 16) moved by NTHREADS threads in 16-byte units, unit i = thread + k * NTHREADS of the row-major
+ * list of units. The loads are issued in start_xfer_async(), i.e. BEFORE the DMA threads wait for
+ * the buffer, the stores after the wait -- the reference's scheme for everything
+ * (cudaDMAv2.h:1461-1475). Loops of small transfers are latency chains (compute releases, DMA
+ * fills, compute consumes), and a copy that may only start once the buffer is free pays a whole
+ * trip to memory per link where the early loads overlap it with the consumer's work on the
+ * previous buffer (the reference's saxpy example, 1 KiB per transfer: 0.39 us per iteration
+ * against 0.19). All indices are compile-time, so the staging array stays in registers.
+ */
+template <int ROW_BYTES, int ROWS, int NTHREADS>
+struct StagedShape {
+  static constexpr int UPR = ROW_BYTES / 16;                             /* units per row */
+  static constexpr int TOTAL = UPR * ROWS;
+  static constexpr int UNITS = NTHREADS > 0 ? (TOTAL + NTHREADS - 1) / NTHREADS : 0; /* per thread */
+};
+template <int ROW_BYTES, int ROWS, int NTHREADS, bool L2_ONLY, int N>
+__device__ __forceinline__ void staged_load(uint4 (&v)[N], const char *src, const long long src_stride, const int tid) {
+  typedef StagedShape<ROW_BYTES, ROWS, NTHREADS> S;
+#pragma unroll
+  for (int k = 0; k < S::UNITS; ++k) {
+    const int i = tid + k * NTHREADS;
+    if ((k + 1) * NTHREADS <= S::TOTAL || i < S::TOTAL) {
+      const int r = i / S::UPR, c = i - r * S::UPR;
+      const uint4 *g = reinterpret_cast<const uint4 *>(src + (long long)r * src_stride + 16 * c);
+      v[k] = L2_ONLY ? __ldcg(g) : *g; /* a plain load works from any address space */
+    }
+  }
+}
+/* direct: destination and its stride are multiples of 16 (else word by word) */
+template <int ROW_BYTES, int ROWS, int NTHREADS, int N>
+__device__ __forceinline__ void staged_store(const uint4 (&v)[N], char *dst, const long long dst_stride, const int tid,
+                                             const bool direct) {
+  typedef StagedShape<ROW_BYTES, ROWS, NTHREADS> S;
+#pragma unroll
+  for (int k = 0; k < S::UNITS; ++k) {
+    const int i = tid + k * NTHREADS;
+    if ((k + 1) * NTHREADS <= S::TOTAL || i < S::TOTAL) {
+      const int r = i / S::UPR, c = i - r * S::UPR;
+      char *d = dst + (long long)r * dst_stride + 16 * c;
+      if (direct) {
+        *reinterpret_cast<uint4 *>(d) = v[k];
+      } else {
+        unsigned int *w = reinterpret_cast<unsigned int *>(d);
+        w[0] = v[k].x; w[1] = v[k].y; w[2] = v[k].z; w[3] = v[k].w;
+      }
+    }
+  }
+}
+
 /* Constructor arguments arrive as 0..8 ints whose meaning depends on the
  * template level; ArgList just holds them. */
 struct ArgList {
@@ -661,8 +756,7 @@ __device__ __forceinline__ ArgList make_args(I... a) {
 
 #define CUDADMA_B200_XFER_OVERLOADS(SRC_DECL, SRC_ARGS)                                                     \
   __device__ __forceinline__ void execute_dma(SRC_DECL, void *__restrict__ dst_ptr) {                       \
-    start_impl<true, LOAD_CACHE_ALL>(SRC_ARGS);                                                             \
-    finish_impl<LOAD_CACHE_ALL>(dst_ptr);                                                                   \
+    execute_impl<true, LOAD_CACHE_ALL>(SRC_ARGS, dst_ptr);                                                  \
   }                                                                                                         \
   __device__ __forceinline__ void start_xfer_async(SRC_DECL) { start_impl<true, LOAD_CACHE_ALL>(SRC_ARGS); } \
   __device__ __forceinline__ void wait_xfer_finish(void *__restrict__ dst_ptr) {                            \
@@ -670,8 +764,7 @@ __device__ __forceinline__ ArgList make_args(I... a) {
   }                                                                                                         \
   template <bool DMA_GLOBAL_LOAD>                                                                           \
   __device__ __forceinline__ void execute_dma(SRC_DECL, void *__restrict__ dst_ptr) {                       \
-    start_impl<DMA_GLOBAL_LOAD, LOAD_CACHE_ALL>(SRC_ARGS);                                                  \
-    finish_impl<LOAD_CACHE_ALL>(dst_ptr);                                                                   \
+    execute_impl<DMA_GLOBAL_LOAD, LOAD_CACHE_ALL>(SRC_ARGS, dst_ptr);                                       \
   }                                                                                                         \
   template <bool DMA_GLOBAL_LOAD>                                                                           \
   __device__ __forceinline__ void start_xfer_async(SRC_DECL) {                                              \
@@ -683,8 +776,7 @@ __device__ __forceinline__ ArgList make_args(I... a) {
   }                                                                                                         \
   template <bool DMA_GLOBAL_LOAD, int DMA_LOAD_QUAL, int DMA_STORE_QUAL>                                    \
   __device__ __forceinline__ void execute_dma(SRC_DECL, void *__restrict__ dst_ptr) {                       \
-    start_impl<DMA_GLOBAL_LOAD, DMA_LOAD_QUAL>(SRC_ARGS);                                                   \
-    finish_impl<DMA_LOAD_QUAL>(dst_ptr);                                                                    \
+    execute_impl<DMA_GLOBAL_LOAD, DMA_LOAD_QUAL>(SRC_ARGS, dst_ptr);                                        \
   }                                                                                                         \
   template <bool DMA_GLOBAL_LOAD, int DMA_LOAD_QUAL, int DMA_STORE_QUAL>                                    \
   __device__ __forceinline__ void start_xfer_async(SRC_DECL) {                                              \
@@ -734,8 +826,25 @@ class CudaDMASequential : public CudaDMA {
     }
     return p;
   }
+  /* Small, fully templated transfers (at most 64 bytes per DMA thread) are staged through registers
+   * (see detail::staged_load), with plain loads and stores, so source and destination may be in
+   * any address space. Such an object never issues an asynchronous copy, so its handshake can use
+   * the hardware barriers (see class CudaDMA). With ALIGNMENT == 16 the object takes the caller's
+   * word for it, as the reference does (a pointer less aligned than promised faults); with
+   * ALIGNMENT 4 or 8 it looks at the pointers and, where they are not 16-byte aligned, copies
+   * with smaller loads and stores after the wait instead. Larger transfers keep the asynchronous
+   * copies, which take whatever alignment they find. */
+  static constexpr int NT = DMA_THREADS > 0 ? DMA_THREADS : 1;
+  static constexpr bool TRUST = ALIGNMENT == 16;
+#if defined(CUDADMA_NO_REGISTER_STAGING) || defined(CUDADMA_CHECKED) /* checked builds move everything through the engine */
+  static constexpr bool STAGED = false;
+#else
+  static constexpr bool STAGED = LEVEL == 3 && BYTES_PER_ELMT % 16 == 0 && BYTES_PER_ELMT <= 64 * NT;
+#endif
+  typedef cudadma_b200::detail::StagedShape<STAGED ? BYTES_PER_ELMT : 16, 1, NT> Shape;
   __device__ __forceinline__ CudaDMASequential(const Params &p, int)
-      : CudaDMA(p.dmaID, p.ndma, p.ncomp, p.start, DO_SYNC), m_bytes(p.bytes), m_src(0), m_staged(false) {}
+      : CudaDMA(p.dmaID, p.ndma, p.ncomp, p.start, DO_SYNC, !STAGED, STAGED), m_bytes(p.bytes), m_src(0),
+        m_staged(false) {}
 
  public:
   template <typename... I>
@@ -747,69 +856,71 @@ class CudaDMASequential : public CudaDMA {
   CUDADMA_B200_XFER_OVERLOADS(const void *__restrict__ src_ptr, src_ptr)
 
  private:
-  /* Small, fully templated, warp-specialised loads (at most 64 bytes per DMA thread) are staged the
-   * way the reference stages everything (cudaDMAv2.h:1461-1475): the DMA threads read the source
-   * into registers in start_xfer_async(), i.e. before they wait for the buffer, and store to shared
-   * memory after the wait. Such loops are latency chains -- compute releases, DMA fills, compute
-   * consumes -- and a copy that only starts after the release costs a second memory round trip per
-   * link (measured on the reference's saxpy example, 1 KiB per transfer: 0.39 us per iteration
-   * against 0.19). Larger transfers keep the asynchronous copies. */
-  static constexpr int PRE_UNITS =
-      (DO_SYNC && LEVEL == 3 && BYTES_PER_ELMT % 16 == 0 && BYTES_PER_ELMT <= 64 * (DMA_THREADS > 0 ? DMA_THREADS : 1))
-          ? (BYTES_PER_ELMT / 16 + (DMA_THREADS > 0 ? DMA_THREADS : 1) - 1) / (DMA_THREADS > 0 ? DMA_THREADS : 1)
-          : 0;
   template <bool GLOBAL, int LQ>
   __device__ __forceinline__ void start_impl(const void *src) {
     m_src = static_cast<const char *>(src);
-    m_staged = false;
-#if !defined(CUDADMA_NO_REGISTER_STAGING) && !defined(CUDADMA_CHECKED) /* checked builds move everything through the engine */
-    if (PRE_UNITS > 0 && GLOBAL && m_is_dma_thread &&
-        (cudadma_b200::detail::addr_bits(src) & 15) == 0 && __isGlobal(src)) {
-#pragma unroll
-      for (int u = 0; u < (PRE_UNITS > 0 ? PRE_UNITS : 1); ++u) {
-        const int off = 16 * (m_dma_tid + u * (DMA_THREADS > 0 ? DMA_THREADS : 1));
-        if (off < BYTES_PER_ELMT) {
-          const uint4 *g = reinterpret_cast<const uint4 *>(m_src + off);
-          m_stage[u] = (LQ == LOAD_CACHE_ALL) ? *g : __ldcg(g);
-        }
-      }
-      m_staged = true;
+    if (STAGED) {
+      m_staged = m_is_dma_thread && (TRUST || (cudadma_b200::detail::addr_bits(src) & 15) == 0);
+      if (m_staged)
+        cudadma_b200::detail::staged_load<STAGED ? BYTES_PER_ELMT : 16, 1, NT, GLOBAL && LQ != LOAD_CACHE_ALL>(m_stage, m_src, 0, m_dma_tid);
       return;
     }
-#endif
     if (DO_SYNC && GLOBAL) cudadma_b200::detail::prefetch_small(m_src, 1, m_bytes, 0, m_dma_tid, m_num_dma_threads);
+  }
+  /* execute_dma: the whole transfer in one call. A staged object keeps the bytes in a local array
+   * here, so that nothing of one transfer stays live into the next (the member array serves the
+   * two-phase calls, where it has to). */
+  template <bool GLOBAL, int LQ>
+  __device__ __forceinline__ void execute_impl(const void *src, void *dst) {
+    using namespace cudadma_b200::detail;
+    if (STAGED) {
+      const char *s = static_cast<const char *>(src);
+      const bool early = m_is_dma_thread && (TRUST || (addr_bits(src) & 15) == 0);
+      uint4 stage[Shape::UNITS > 0 ? Shape::UNITS : 1];
+      if (early) staged_load<STAGED ? BYTES_PER_ELMT : 16, 1, NT, GLOBAL && LQ != LOAD_CACHE_ALL>(stage, s, 0, m_dma_tid);
+      if (DO_SYNC) wait_for_dma_start_for_stores();
+      else if (!m_is_dma_thread) return;
+      if (early) {
+        staged_store<STAGED ? BYTES_PER_ELMT : 16, 1, NT>(stage, static_cast<char *>(dst), 0, m_dma_tid,
+                                                          TRUST || (addr_bits(dst) & 15) == 0);
+      } else if (!TRUST && m_is_dma_thread) {
+        StridedRows a = {s, static_cast<char *>(dst), 0, 0};
+        generic_rows(a, 1, m_bytes, copy_unit(addr_bits(s) | addr_bits(dst) | (unsigned long long)m_bytes), m_dma_tid,
+                     m_num_dma_threads);
+      }
+      if (DO_SYNC) finish_async_dma();
+      return;
+    }
+    start_impl<GLOBAL, LQ>(src);
+    finish_impl<LQ>(dst);
   }
   template <int LQ>
   __device__ __forceinline__ void finish_impl(void *dst) {
-    if (PRE_UNITS > 0 && m_staged) wait_for_dma_start_for_stores();
-    else if (DO_SYNC) wait_for_dma_start();
-    else if (!m_is_dma_thread) return;
-    if (PRE_UNITS > 0 && m_staged) {
-      /* all DMA threads of the object take the same branch: the test is on the two pointers only */
-      char *d = static_cast<char *>(dst);
-      const bool direct = (cudadma_b200::detail::addr_bits(dst) & 15) == 0;
-#pragma unroll
-      for (int u = 0; u < (PRE_UNITS > 0 ? PRE_UNITS : 1); ++u) {
-        const int off = 16 * (m_dma_tid + u * (DMA_THREADS > 0 ? DMA_THREADS : 1));
-        if (off < BYTES_PER_ELMT) {
-          if (direct) {
-            *reinterpret_cast<uint4 *>(d + off) = m_stage[u];
-          } else {
-            unsigned int *w = reinterpret_cast<unsigned int *>(d + off);
-            w[0] = m_stage[u].x; w[1] = m_stage[u].y; w[2] = m_stage[u].z; w[3] = m_stage[u].w;
-          }
-        }
+    using namespace cudadma_b200::detail;
+    if (STAGED) {
+      /* all DMA threads of the object take the same branches: the tests are on the two pointers only */
+      if (DO_SYNC) wait_for_dma_start_for_stores();
+      else if (!m_is_dma_thread) return;
+      if (m_staged) {
+        staged_store<STAGED ? BYTES_PER_ELMT : 16, 1, NT>(m_stage, static_cast<char *>(dst), 0, m_dma_tid,
+                                                          TRUST || (addr_bits(dst) & 15) == 0);
+      } else if (!TRUST && m_is_dma_thread) {
+        StridedRows a = {m_src, static_cast<char *>(dst), 0, 0};
+        generic_rows(a, 1, m_bytes, copy_unit(addr_bits(m_src) | addr_bits(dst) | (unsigned long long)m_bytes), m_dma_tid,
+                     m_num_dma_threads);
       }
-      finish_async_dma();
+      if (DO_SYNC) finish_async_dma();
       return;
     }
-    const int pending = cudadma_b200::detail::issue_contiguous<DO_SYNC, LQ>(
-        m_src, static_cast<char *>(dst), m_bytes, m_dma_tid, m_num_dma_threads, m_bar_full);
-    cudadma_b200::detail::complete<DO_SYNC>(pending, m_bar_full);
+    if (DO_SYNC) wait_for_dma_start();
+    else if (!m_is_dma_thread) return;
+    const int pending = issue_contiguous<DO_SYNC, LQ>(m_src, static_cast<char *>(dst), m_bytes, m_dma_tid,
+                                                      m_num_dma_threads, m_bar_full);
+    complete<DO_SYNC>(pending, m_bar_full);
   }
   const int m_bytes;
   const char *m_src;
-  uint4 m_stage[PRE_UNITS > 0 ? PRE_UNITS : 1];
+  uint4 m_stage[Shape::UNITS > 0 ? Shape::UNITS : 1];
   bool m_staged;
 };
 
@@ -899,9 +1010,24 @@ class CudaDMAStrided : public CudaDMA {
     }
     return p;
   }
+  /* Small, fully templated tiles are staged through registers like small CudaDMASequential
+   * transfers (see detail::staged_load): at most BYTES_PER_THREAD bytes per DMA thread, which is
+   * what that parameter bounds in the reference too, and never more than 128. Such an object issues
+   * no asynchronous copy, so its handshake can use the hardware barriers (see class CudaDMA). */
+  static constexpr int NT = DMA_THREADS > 0 ? DMA_THREADS : 1;
+  typedef cudadma_b200::detail::StagedShape<(LEVEL == 4 && BYTES_PER_ELMT % 16 == 0) ? BYTES_PER_ELMT : 16,
+                                            LEVEL == 4 ? NUM_ELMTS : 1, NT> Shape;
+#if defined(CUDADMA_NO_REGISTER_STAGING) || defined(CUDADMA_CHECKED)
+  static constexpr bool STAGED = false;
+#else
+  static constexpr bool STAGED = LEVEL == 4 && BYTES_PER_ELMT % 16 == 0 &&
+                                 16 * Shape::UNITS <= (BYTES_PER_THREAD < 128 ? BYTES_PER_THREAD : 128);
+#endif
+  static constexpr int SB = STAGED ? BYTES_PER_ELMT : 16, SR = STAGED ? NUM_ELMTS : 1; /* staged shape */
+  static constexpr bool TRUST = ALIGNMENT == 16; /* pointers and strides are what the template argument says */
   __device__ __forceinline__ CudaDMAStrided(const Params &p, int)
-      : CudaDMA(p.dmaID, p.ndma, p.ncomp, p.start, DO_SYNC), m_bytes(p.bytes), m_rows(p.rows),
-        m_src_stride(p.sstride), m_dst_stride(p.dstride), m_src(0) {}
+      : CudaDMA(p.dmaID, p.ndma, p.ncomp, p.start, DO_SYNC, !STAGED, STAGED), m_bytes(p.bytes), m_rows(p.rows),
+        m_src_stride(p.sstride), m_dst_stride(p.dstride), m_src(0), m_staged(false) {}
 
  public:
   template <typename... I>
@@ -921,6 +1047,8 @@ class CudaDMAStrided : public CudaDMA {
                                                      const int nboxes, const int box_cols,
                                                      const uint32_t box_bytes) {
     static_assert(DO_SYNC, "tensor-map transfers need a warp-specialised object");
+    static_assert(!STAGED, "this instantiation is small enough to be staged through registers and has no mbarrier "
+                           "for a tensor-map transfer to count on; build with -DCUDADMA_NO_REGISTER_STAGING");
     wait_for_dma_start();
     if (m_dma_tid == 0) {
       cudadma_b200::ptx::mbar_expect_tx(m_bar_full, box_bytes * (uint32_t)nboxes);
@@ -935,12 +1063,62 @@ class CudaDMAStrided : public CudaDMA {
   template <bool GLOBAL, int LQ>
   __device__ __forceinline__ void start_impl(const void *src) {
     m_src = static_cast<const char *>(src);
+    if (STAGED) {
+      m_staged = m_is_dma_thread &&
+                 (TRUST || ((cudadma_b200::detail::addr_bits(src) | (unsigned long long)(unsigned)m_src_stride) & 15) == 0);
+      if (m_staged)
+        cudadma_b200::detail::staged_load<SB, SR, NT, GLOBAL && LQ != LOAD_CACHE_ALL>(m_stage, m_src, m_src_stride, m_dma_tid);
+      return;
+    }
     if (DO_SYNC && GLOBAL)
       cudadma_b200::detail::prefetch_small(m_src, m_rows, m_bytes, m_src_stride, m_dma_tid, m_num_dma_threads);
+  }
+  /* execute_dma in one call; a staged object keeps the bytes in a local array (see CudaDMASequential) */
+  template <bool GLOBAL, int LQ>
+  __device__ __forceinline__ void execute_impl(const void *src, void *dst) {
+    using namespace cudadma_b200::detail;
+    if (STAGED) {
+      const char *s = static_cast<const char *>(src);
+      const bool early = m_is_dma_thread &&
+                         (TRUST || ((addr_bits(src) | (unsigned long long)(unsigned)m_src_stride) & 15) == 0);
+      uint4 stage[STAGED ? Shape::UNITS : 1];
+      if (early) staged_load<SB, SR, NT, GLOBAL && LQ != LOAD_CACHE_ALL>(stage, s, m_src_stride, m_dma_tid);
+      if (DO_SYNC) wait_for_dma_start_for_stores();
+      else if (!m_is_dma_thread) return;
+      const unsigned long long dmask = addr_bits(dst) | (unsigned long long)(unsigned)m_dst_stride;
+      if (early) {
+        staged_store<SB, SR, NT>(stage, static_cast<char *>(dst), m_dst_stride, m_dma_tid, TRUST || (dmask & 15) == 0);
+      } else if (!TRUST && m_is_dma_thread) {
+        StridedRows a = {s, static_cast<char *>(dst), m_src_stride, m_dst_stride};
+        generic_rows(a, m_rows, m_bytes,
+                     copy_unit(dmask | addr_bits(s) | (unsigned long long)(unsigned)m_src_stride | (unsigned long long)m_bytes),
+                     m_dma_tid, m_num_dma_threads);
+      }
+      if (DO_SYNC) finish_async_dma();
+      return;
+    }
+    start_impl<GLOBAL, LQ>(src);
+    finish_impl<LQ>(dst);
   }
   template <int LQ>
   __device__ __forceinline__ void finish_impl(void *dst) {
     using namespace cudadma_b200::detail;
+    if (STAGED) {
+      if (DO_SYNC) wait_for_dma_start_for_stores();
+      else if (!m_is_dma_thread) return;
+      const unsigned long long dmask = addr_bits(dst) | (unsigned long long)(unsigned)m_dst_stride;
+      if (m_staged) {
+        staged_store<SB, SR, NT>(m_stage, static_cast<char *>(dst), m_dst_stride, m_dma_tid, TRUST || (dmask & 15) == 0);
+      } else if (!TRUST && m_is_dma_thread) {
+        StridedRows a = {m_src, static_cast<char *>(dst), m_src_stride, m_dst_stride};
+        generic_rows(a, m_rows, m_bytes,
+                     copy_unit(dmask | addr_bits(m_src) | (unsigned long long)(unsigned)m_src_stride |
+                               (unsigned long long)m_bytes),
+                     m_dma_tid, m_num_dma_threads);
+      }
+      if (DO_SYNC) finish_async_dma();
+      return;
+    }
     if (DO_SYNC) wait_for_dma_start();
     else if (!m_is_dma_thread) return;
     int pending;
@@ -961,6 +1139,8 @@ class CudaDMAStrided : public CudaDMA {
   const int m_src_stride;
   const int m_dst_stride;
   const char *m_src;
+  uint4 m_stage[STAGED ? Shape::UNITS : 1];
+  bool m_staged;
 };
 
 template <bool DO_SYNC>
@@ -1032,8 +1212,14 @@ class CudaDMAIndirect : public CudaDMA {
     }
     return p;
   }
+  /* records shorter than the smallest bulk copy never meet the bulk-copy engine */
+#ifdef CUDADMA_ALWAYS_FENCE
+  static constexpr bool MAY_BULK = true;
+#else
+  static constexpr bool MAY_BULK = !(BYTES_PER_ELMT > 0 && BYTES_PER_ELMT < CUDADMA_BULK_ROW_MIN);
+#endif
   __device__ __forceinline__ CudaDMAIndirect(const Params &p, int)
-      : CudaDMA(p.dmaID, p.ndma, p.ncomp, p.start, DO_SYNC), m_bytes(p.bytes), m_rows(p.rows),
+      : CudaDMA(p.dmaID, p.ndma, p.ncomp, p.start, DO_SYNC, MAY_BULK), m_bytes(p.bytes), m_rows(p.rows),
         m_pitch(p.alt > p.bytes ? p.alt : p.bytes), m_index(0), m_src(0) {}
 
  public:
@@ -1053,6 +1239,7 @@ class CudaDMAIndirect : public CudaDMA {
                                                       void *dst) {
     static_assert(DO_SYNC && GATHER, "gather4 needs a warp-specialised gather object");
     wait_for_dma_start();
+    if (!MAY_BULK) cudadma_b200::ptx::fence_proxy_async();
     const int groups = m_rows >> 2;
     const int mine = (groups > m_dma_tid) ? (groups - m_dma_tid + m_num_dma_threads - 1) / m_num_dma_threads : 0;
     if (mine > 0) {
@@ -1075,6 +1262,7 @@ class CudaDMAIndirect : public CudaDMA {
                                                        const void *src) {
     static_assert(DO_SYNC && !GATHER, "scatter4 needs a warp-specialised scatter object");
     wait_for_dma_start();
+    if (!MAY_BULK) cudadma_b200::ptx::fence_proxy_async(); /* the rows were written by ordinary or cp.async stores */
     const int groups = m_rows >> 2;
     const uint32_t s0 = cudadma_b200::ptx::smem_u32(src);
     for (int g = m_dma_tid; g < groups; g += m_num_dma_threads) {
@@ -1091,6 +1279,11 @@ class CudaDMAIndirect : public CudaDMA {
   __device__ __forceinline__ void start_impl(const int *index, const void *src) {
     m_index = index;
     m_src = static_cast<const char *>(src);
+  }
+  template <bool GLOBAL, int LQ>
+  __device__ __forceinline__ void execute_impl(const int *index, const void *src, void *dst) {
+    start_impl<GLOBAL, LQ>(index, src);
+    finish_impl<LQ>(dst);
   }
   template <int LQ>
   __device__ __forceinline__ void finish_impl(void *dst) {
@@ -1232,13 +1425,17 @@ using cudaDMAHalo = CudaDMAHalo<ELMT_TYPE, RADIUS, CORNERS, ALIGNMENT>;
 
 /* ------------------------------------------------------------------------- */
 /* CudaDMACustom: only the handshake, for hand-written copy loops             */
-/* (v1 cudaDMACustom, cudaDMA.h:4184-4208).                                   */
+/* (v1 cudaDMACustom, cudaDMA.h:4184-4208). The caller's loop fills the buffer */
+/* with ordinary stores, so the handshake is a pair of hardware barriers where */
+/* dmaID and thread counts allow it (see class CudaDMA). A caller that fills   */
+/* the buffer with asynchronous copies of its own must wait for them before    */
+/* finish_async_dma().                                                         */
 /* ------------------------------------------------------------------------- */
 class CudaDMACustom : public CudaDMA {
  public:
   __device__ __forceinline__ CudaDMACustom(const int dmaID, const int num_dma_threads, const int num_compute_threads,
                                            const int dma_threadIdx_start)
-      : CudaDMA(dmaID, num_dma_threads, num_compute_threads, dma_threadIdx_start, true) {}
+      : CudaDMA(dmaID, num_dma_threads, num_compute_threads, dma_threadIdx_start, true, false, true) {}
 };
 typedef CudaDMACustom cudaDMACustom;
 

@@ -24,31 +24,49 @@ int sm_count() {
 }
 }  // namespace
 
+/* BYTES_PER_THREAD of the objects, the reference's register staging budget: 64, 128 or 192 */
+#define BPT_DISPATCH(bpt, CALL)                    \
+  switch (bpt) {                                   \
+    case 64: return CALL(64);                      \
+    case 128: return CALL(128);                    \
+    case 192: return CALL(192);                    \
+    default: return (int)cudaErrorInvalidValue;    \
+  }
+
 extern "C" {
 
-int cudadma_ref_seq_copy(void *dst, const void *src, size_t bytes, void *stream) {
+int cudadma_ref_seq_copy(void *dst, const void *src, size_t bytes, int bpt, void *stream) {
   if (bytes % portable::P_CHUNK) return (int)cudaErrorInvalidValue;
-  return portable::launch_seq_copy(static_cast<char *>(dst), static_cast<const char *>(src),
-                                   (long long)(bytes / portable::P_CHUNK), sm_count(), (cudaStream_t)stream);
+#define CALL(B) portable::launch_seq_copy<B>(static_cast<char *>(dst), static_cast<const char *>(src), \
+                                             (long long)(bytes / portable::P_CHUNK), sm_count(), (cudaStream_t)stream)
+  BPT_DISPATCH(bpt, CALL)
+#undef CALL
 }
 
-int cudadma_ref_strided_transpose(float *dst, const float *src, int rows, int cols, void *stream) {
+int cudadma_ref_strided_transpose(float *dst, const float *src, int rows, int cols, int bpt, void *stream) {
   if (rows % portable::PT_ROWS || cols % portable::PT_COLS) return (int)cudaErrorInvalidValue;
-  return portable::launch_transpose(dst, src, rows, cols, sm_count(), (cudaStream_t)stream);
+#define CALL(B) portable::launch_transpose<B>(dst, src, rows, cols, sm_count(), (cudaStream_t)stream)
+  BPT_DISPATCH(bpt, CALL)
+#undef CALL
 }
 
 int cudadma_ref_gather_scatter(void *out, const void *table, const int *gather_idx, const int *scatter_idx, size_t n,
-                               void *stream) {
+                               int bpt, void *stream) {
   if (n % 128) return (int)cudaErrorInvalidValue;
-  return portable::launch_gather_scatter(static_cast<char *>(out), static_cast<const char *>(table), gather_idx,
-                                         scatter_idx, (long long)(n / 128), sm_count(), (cudaStream_t)stream);
+  /* 32-byte records: the reference wants BYTES_PER_THREAD / ALIGNMENT loads per thread, all three budgets are legal */
+#define CALL(B) portable::launch_gather_scatter<32, B>(static_cast<char *>(out), static_cast<const char *>(table), gather_idx, \
+                                                       scatter_idx, (long long)(n / 128), sm_count(), (cudaStream_t)stream)
+  BPT_DISPATCH(bpt, CALL)
+#undef CALL
 }
 
 /* arrays padded by four zero cells on every side: (nx + 8) x (ny + 8) x (nz + 8) floats */
 int cudadma_ref_stencil25_step_padded(float *out, const float *in, int nx, int ny, int nz, int z_begin, int z_end,
-                                      const float coeff[5], int z_chunk, void *stream) {
-  return portable::launch_stencil_padded(out, in, nx, ny, nz, z_begin, z_end, coeff, z_chunk, sm_count(),
-                                         (cudaStream_t)stream);
+                                      const float coeff[5], int z_chunk, int bpt, void *stream) {
+#define CALL(B) portable::launch_stencil_padded<B>(out, in, nx, ny, nz, z_begin, z_end, coeff, z_chunk, sm_count(), \
+                                                   (cudaStream_t)stream)
+  BPT_DISPATCH(bpt, CALL)
+#undef CALL
 }
 
 } /* extern "C" */

@@ -108,3 +108,19 @@ def test_reference_v1_saxpy_example_runs_unchanged_on_this_header(example, kerne
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
     exact = np.float64(np.float32(a)) * x.astype(np.float64) + y.astype(np.float64)
     assert np.allclose(got, exact, rtol=1e-6, atol=0.0)
+
+
+@pytest.mark.parametrize("kernel_id", range(4))
+def test_reference_throughput_benchmark_runs_unchanged_on_this_header(kernel_id):
+    """src/perf/sequential/perf_sequential.cu (non_specialized, single_buffer, double_buffer, manual_buffer,
+    written against v1 cudaDMASequential) built unmodified against both headers (oracle/ref_perf_sequential.cu).
+    Its kernels load into shared memory and write nothing back, as the reference measures them, so there are
+    no bits to compare: both builds must run to completion with no wait giving up, and report a bandwidth."""
+    from oracle import examples
+    if not examples.available("libperfseq_ours.so", "libperfseq_ref.so"):
+        pytest.skip("perf_sequential libraries not built")
+    ours, ms_ours = examples.run_perf_sequential("ours", kernel_id)
+    ref, ms_ref = examples.run_perf_sequential("ref", kernel_id)
+    print("perf_sequential %s: %.0f GB/s on this header, %.0f GB/s on the reference header"
+          % (examples.PERFSEQ_NAMES[kernel_id], ours, ref))
+    assert ours > 0 and ref > 0 and ms_ours > 0 and ms_ref > 0

@@ -77,3 +77,49 @@ def test_stencil_matches_reference_build():
     exp = oracle.stencil25_f64(field, cd.STENCIL_COEFFS, 1)
     got = a[4:-4, 4:-4, 4:-4].cpu().numpy()
     assert np.abs(got - exp).max() / np.abs(exp).max() <= 1e-5
+
+
+@pytest.mark.parametrize("bpt", ref.BPTS)
+def test_every_staging_budget_of_the_reference_arm_gives_the_same_bits(bpt):
+    """The reference arm of the benchmark tries BYTES_PER_THREAD = 64, 128 and 192 and keeps the fastest:
+    each must be the same copy, transpose and stencil."""
+    n = 16384 * 40
+    src = dev(oracle.fill_uniform(n // 4, 0xC1, -1.0, 1.0))
+    a = torch.zeros_like(src)
+    ref.seq_copy(a, src, n, bpt)
+    assert torch.equal(a.view(torch.int32), src.view(torch.int32))
+    rows, cols = 256, 192
+    m = dev(oracle.fill_uniform(rows * cols, 0xC2, -1.0, 1.0))
+    t = torch.zeros_like(m)
+    ref.strided_transpose(t, m, rows, cols, bpt)
+    assert torch.equal(t.view(cols, rows), m.view(rows, cols).t())
+    nx, ny, nz = 64, 32, 20
+    pad = torch.zeros((nz + 8, ny + 8, nx + 8), dtype=torch.float32, device="cuda")
+    pad[4:-4, 4:-4, 4:-4] = dev(oracle.fill_uniform(nx * ny * nz, 0xC4, 0.0, 1.0)).view(nz, ny, nx)
+    x, y = torch.zeros_like(pad), torch.zeros_like(pad)
+    ref.stencil25_step_padded(x, pad, nx, ny, nz, 0, nz, cd.STENCIL_COEFFS, 0, bpt)
+    cd.stencil25_step_padded(y, pad, nx, ny, nz, 0, nz)
+    assert torch.equal(x.view(torch.int32), y.view(torch.int32))
+
+
+def test_halo_ring_stencil_matches_on_both_headers():
+    """oracle/ref_halo_stencil.cu: ring by v1 cudaDMAHalo, interior by cudaDMAStrided. Built against the
+    reference's v1 header and against this repository's header it gives the same bits, and those are the
+    bits of the window-loading stencil (same arithmetic source)."""
+    import os
+    ours_path = os.path.join(os.path.dirname(ref.HALO_STENCIL_PATH), "libhalo_stencil_ours.so")
+    if not (ref.halo_stencil_available() and os.path.exists(ours_path)):
+        pytest.skip("halo stencil libraries not built")
+    ours = ref.halo_lib(ours_path)
+    for nx, ny, nz, zb, ze in ((64, 32, 20, 0, 20), (128, 64, 41, 3, 38), (32, 16, 9, 0, 9)):
+        pad = torch.zeros((nz + 8, ny + 8, nx + 8), dtype=torch.float32, device="cuda")
+        pad[4:-4, 4:-4, 4:-4] = dev(oracle.fill_uniform(nx * ny * nz, 0xC4, 0.0, 1.0)).view(nz, ny, nx)
+        a, b, c = (torch.zeros_like(pad) for _ in range(3))
+        ref.halo_stencil25_step_padded(a, pad, nx, ny, nz, zb, ze, cd.STENCIL_COEFFS)
+        ref.halo_stencil25_step_padded(b, pad, nx, ny, nz, zb, ze, cd.STENCIL_COEFFS, lib_handle=ours)
+        cd.stencil25_step_padded(c, pad, nx, ny, nz, zb, ze)
+        torch.cuda.synchronize()
+        assert torch.equal(b.view(torch.int32), c.view(torch.int32)), "this header: ring + interior against whole windows"
+        assert torch.equal(a.view(torch.int32), c.view(torch.int32)), "reference header"
+    w = __import__("ctypes").c_uint(0)
+    assert ours.halo_stencil_status(__import__("ctypes").byref(w)) == 0 and w.value == 0
