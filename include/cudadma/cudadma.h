@@ -322,9 +322,10 @@ __device__ __forceinline__ uint32_t barrier_addr(int dmaID, int which) {
 }
 
 /* Slow half of a wait: keeps polling, gives up after CUDADMA_WAIT_LIMIT_CYCLES
- * or as soon as any earlier wait of the grid has given up. (Sleeping between polls, 32 to 256 ns,
+ * or as soon as any earlier wait of the grid has given up. (Sleeping between polls, 32 ns to 2 us,
  * and a suspend-time hint on the poll were both measured on the stencil kernel, whose DMA warps
- * wait most of the time: no gain from the first, a 1 % loss from the second.) */
+ * wait most of the time, also with the GPU at its power cap: no gain from the first, a 1 % loss
+ * from the second.) */
 inline __device__ __noinline__ void wait_slow(uint32_t bar, uint32_t parity, unsigned int code) {
   const long long t0 = clock64();
   unsigned int polls = 0;
@@ -875,7 +876,8 @@ class CudaDMASequential : public CudaDMA {
     using namespace cudadma_b200::detail;
     if (STAGED) {
       const char *s = static_cast<const char *>(src);
-      const bool early = m_is_dma_thread && (TRUST || (addr_bits(src) & 15) == 0);
+      /* warp-specialised: only DMA threads call this (the reference's contract); otherwise every thread does */
+      const bool early = (DO_SYNC || m_is_dma_thread) && (TRUST || (addr_bits(src) & 15) == 0);
       uint4 stage[Shape::UNITS > 0 ? Shape::UNITS : 1];
       if (early) staged_load<STAGED ? BYTES_PER_ELMT : 16, 1, NT, GLOBAL && LQ != LOAD_CACHE_ALL>(stage, s, 0, m_dma_tid);
       if (DO_SYNC) wait_for_dma_start_for_stores();
@@ -1079,7 +1081,7 @@ class CudaDMAStrided : public CudaDMA {
     using namespace cudadma_b200::detail;
     if (STAGED) {
       const char *s = static_cast<const char *>(src);
-      const bool early = m_is_dma_thread &&
+      const bool early = (DO_SYNC || m_is_dma_thread) &&
                          (TRUST || ((addr_bits(src) | (unsigned long long)(unsigned)m_src_stride) & 15) == 0);
       uint4 stage[STAGED ? Shape::UNITS : 1];
       if (early) staged_load<SB, SR, NT, GLOBAL && LQ != LOAD_CACHE_ALL>(stage, s, m_src_stride, m_dma_tid);

@@ -112,8 +112,8 @@ int cudadma_gather_scatter(void *out, const void *table, const int32_t *gather_i
  * through ... tile::scatter4 (execute_dma_scatter4); mode 1, 2 or 3. The tensor maps need the
  * extents of table and output, hence table_records and out_records. Same result as
  * cudadma_gather_scatter, which stays the default path: on B200 neither TMA form was faster than
- * its 16-byte cp.async gather and 16-byte stores (figures with the benchmark configuration are in
- * the repository's design notes). gather_idx entries must be < table_records, scatter_idx
+ * its 16-byte cp.async gather and 16-byte stores (benchmark configuration, same CTAs per SM: 1.81
+ * TB/s with row gathers, 1.73 with row scatters, 1.73 without). gather_idx entries must be < table_records, scatter_idx
  * entries < out_records; record_bytes must be 32. */
 int cudadma_gather_scatter_tma(void *out, size_t out_records, const void *table, size_t table_records,
                                const int32_t *gather_idx, const int32_t *scatter_idx, size_t n, int record_bytes,
