@@ -60,6 +60,7 @@ SYMBOLS = [
     ("cudadma_slab_connect", _c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p]),
     ("cudadma_slab_connect_local", _c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p]),
     ("cudadma_slab_set_wait_limit", _c.c_int, [_c.c_void_p, _c.c_longlong]),
+    ("cudadma_slab_set_edge_planes", _c.c_int, [_c.c_void_p, _c.c_int]),
     ("cudadma_slab_buffer", _c.c_int, [_c.c_void_p, _c.c_int, _c.POINTER(_c.c_void_p)]),
     ("cudadma_slab_step", _c.c_int, [_c.c_void_p, _c.POINTER(_c.c_float), _c.c_void_p]),
     ("cudadma_slab_status", _c.c_int, [_c.c_void_p, _c.c_void_p]),
@@ -316,6 +317,9 @@ class Slab:
 
     def set_wait_limit(self, sm_cycles):
         _check("cudadma_slab_set_wait_limit", lib().cudadma_slab_set_wait_limit(self._h, int(sm_cycles)))
+
+    def set_edge_planes(self, planes):
+        _check("cudadma_slab_set_edge_planes", lib().cudadma_slab_set_edge_planes(self._h, int(planes)))
 
     def status(self, stream=None):
         """Synchronises the stream; OK, or ERR_TIMEOUT once a wait for a neighbour has given up."""

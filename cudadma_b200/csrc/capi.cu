@@ -55,6 +55,10 @@
 #define STENCIL_MAX_RUN 128 /* longest run of planes the automatic z_chunk gives one CTA (see plan_chunks) */
 #endif
 
+/* Waits inside this library's kernels give up after about four seconds; the wait of a sharded
+ * rank for its neighbours (SLAB_WAIT_LIMIT_CYCLES, about two) is the shorter one, so that a
+ * neighbour that is late is reported as that and not as a starved buffer. */
+#define CUDADMA_WAIT_LIMIT_CYCLES (1ll << 33)
 #include "cudadma.h"
 #include "common_kernels.cuh"
 #include "dma_kernels.cuh"
@@ -777,6 +781,7 @@ struct Slab {
   int cur;                      /* buf[cur] holds the current field */
   unsigned int step;            /* steps finished */
   long long wait_limit;         /* SM cycles a boundary CTA waits for a neighbour */
+  int edge;                     /* depth of the two boundary runs of a step (0: equal runs) */
   bool failed;                  /* a failure word was read back: no further steps */
 };
 
@@ -793,6 +798,7 @@ int cudadma_slab_create(void **out, int nx, int ny, int nzl, int has_lower, int 
   sl->nx = nx; sl->ny = ny; sl->nzl = nzl;
   sl->has_lo = has_lower != 0; sl->has_hi = has_upper != 0;
   sl->wait_limit = SLAB_WAIT_LIMIT_CYCLES;
+  sl->edge = SLAB_EDGE_PLANES;
   const size_t bytes = (size_t)nx * ny * (nzl + 8) * sizeof(float);
   cudaError_t e = cudaMalloc(&sl->buf[0], bytes);
   if (e == cudaSuccess) e = cudaMalloc(&sl->buf[1], bytes);
@@ -890,6 +896,13 @@ int cudadma_slab_set_wait_limit(void *slab, long long sm_cycles) {
   return CUDADMA_OK;
 }
 
+int cudadma_slab_set_edge_planes(void *slab, int planes) {
+  Slab *sl = static_cast<Slab *>(slab);
+  if (!sl || planes < 0 || (planes > 0 && planes < 8)) return CUDADMA_ERR_ARG;
+  sl->edge = planes;
+  return CUDADMA_OK;
+}
+
 int cudadma_slab_buffer(void *slab, int which, float **ptr) {
   Slab *sl = static_cast<Slab *>(slab);
   if (!sl || !ptr || which < 0 || which > 1) return CUDADMA_ERR_ARG;
@@ -927,7 +940,7 @@ int cudadma_slab_step(void *slab, const float coeff[5], void *stream) {
     sync.wait_limit = sl->wait_limit;
   }
   if (int r = launch_stencil_native(nxt, peer, sync, cur, nx, ny, nzt, first, last, coeff, 0,
-                                    (sl->has_lo || sl->has_hi) ? SLAB_EDGE_PLANES : 0, s))
+                                    (sl->has_lo || sl->has_hi) ? sl->edge : 0, s))
     return r;
   sl->cur ^= 1;
   sl->step += 1;

@@ -24,9 +24,11 @@ namespace kernels {
 /* Chunk c of the array is handled by CTA c % gridDim.x.                     */
 /* BULK_STORE: one compute thread writes a chunk back with a bulk store;     */
 /* otherwise all compute threads copy it with 16-byte loads and stores.      */
-/* (Handing a buffer back one chunk late, so that the storing thread waits   */
-/* for the read of the PREVIOUS chunk's store instead of its own, measured   */
-/* 1 to 3 % slower on 1 GiB with four to seven buffers: not kept.)           */
+/* (Measured and not kept: handing a buffer back one chunk late, so that the  */
+/* storing thread waits for the read of the PREVIOUS chunk's store, 1 to 3 % */
+/* slower on 1 GiB with four to seven buffers; L2 evict-first hints on the   */
+/* loads, the stores or both, 0 to 2 % slower; 2 to 4 buffers x 2 to 4 CTAs  */
+/* per SM, and plain 16-byte stores for the write-back, all within 3 % below.)*/
 /* ------------------------------------------------------------------------ */
 constexpr int SEQ_DMA_THREADS = 128;
 constexpr int SEQ_COMPUTE_THREADS = 256;

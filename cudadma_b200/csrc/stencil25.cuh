@@ -239,10 +239,10 @@ __device__ __forceinline__ void compute_side(RING &ring, const unsigned char *sm
     }
     if (sync.ticket) {
       /* This CTA is done with the ghost planes and with its stores into the neighbours. All its
-       * compute threads meet at a hardware barrier (id 15, which no object uses); thread 0 then
+       * compute threads meet at hardware barrier 1 (the objects of this kernel are on mbarriers); thread 0 then
        * makes their stores visible system-wide (the fence is cumulative over what the barrier
        * ordered before it) and takes a ticket; the last boundary CTA of the launch publishes. */
-      asm volatile("bar.sync 15, %0;" ::"n"(COMPUTE_THREADS) : "memory");
+      asm volatile("bar.sync 1, %0;" ::"n"(COMPUTE_THREADS) : "memory");
       if (threadIdx.x == 0) {
         __threadfence_system();
         const unsigned int t = atomicAdd(sync.ticket, 1u);
@@ -266,29 +266,31 @@ __device__ __forceinline__ void compute_side(RING &ring, const unsigned char *sm
 /* DMA side of a boundary CTA, before its first load: wait until the neighbour on that side has
  * finished `step` steps (see Sync). One lane polls with system-scope acquire loads; the fence
  * afterwards orders the TMA loads of the ghost planes (asynchronous proxy) behind the acquire. */
-__device__ __noinline__ void poll_neighbour(const unsigned int *flag, const Sync &sync, const unsigned int side) {
+__device__ __noinline__ bool poll_neighbour(const unsigned int *flag, const Sync &sync, const unsigned int side) {
   const long long t0 = clock64();
   for (;;) {
     unsigned int v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-    if (v >= sync.step) return;
+    if (v >= sync.step) return true;
     if (*reinterpret_cast<volatile unsigned int *>(&cudadma_b200::g_status_word) != 0u ||
         *reinterpret_cast<volatile unsigned int *>(sync.failed) != 0u)
-      return; /* the step is lost already: do not sit out another limit */
+      return false; /* the step is lost already: do not sit out another limit */
     if (clock64() - t0 > sync.wait_limit) {
       atomicCAS(&cudadma_b200::g_status_word, 0u, 0x80000000u | 0xE000u | side);
-      return;
+      return false;
     }
     __nanosleep(100);
   }
 }
-__device__ __forceinline__ void wait_for_neighbours(const Sync &sync, const bool lo, const bool hi) {
+/* whole warp; returns whether the neighbours asked for have arrived */
+__device__ __forceinline__ bool wait_for_neighbours(const Sync &sync, const bool lo, const bool hi) {
+  int ok = 1;
   if ((threadIdx.x & 31) == 0) {
-    if (lo && sync.wait_lo) poll_neighbour(sync.wait_lo, sync, 0u);
-    if (hi && sync.wait_hi) poll_neighbour(sync.wait_hi, sync, 1u);
+    if (lo && sync.wait_lo) ok = poll_neighbour(sync.wait_lo, sync, 0u);
+    if (ok && hi && sync.wait_hi) ok = poll_neighbour(sync.wait_hi, sync, 1u);
     asm volatile("fence.proxy.async;" ::: "memory");
   }
-  __syncwarp();
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
 /* in_map: 3-D tensor map over the nx x ny x nz input (x fastest), box 40 x 40 x 1.
@@ -331,7 +333,10 @@ tensor_kernel(const __grid_constant__ CUtensorMap in_map, float *__restrict__ ou
   /* CTAs whose planes reach into a pushed range are the ones that touch a shared boundary */
   const bool at_lo = peer.lo && z0 < peer.lo_end, at_hi = peer.hi && z0 + depth > peer.hi_begin;
   if (ring.stage[0].owns_this_thread()) {
-    if ((at_lo || at_hi) && sync.ticket) wait_for_neighbours(sync, at_lo, at_hi);
+    /* A neighbour that did not arrive: nothing is loaded at all, so nothing can still be on its way
+     * into shared memory when this CTA's compute threads, whose own waits now give up at once,
+     * have run through their planes and the CTA retires. */
+    if ((at_lo || at_hi) && sync.ticket && !wait_for_neighbours(sync, at_lo, at_hi)) return;
     for (int k0 = 0;; k0 += STAGES) {
 #pragma unroll
       for (int s = 0; s < STAGES; ++s) {

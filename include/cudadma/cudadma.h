@@ -322,26 +322,30 @@ __device__ __forceinline__ uint32_t barrier_addr(int dmaID, int which) {
 }
 
 /* Slow half of a wait: keeps polling, gives up after CUDADMA_WAIT_LIMIT_CYCLES
- * or as soon as any earlier wait of the grid has given up. (Sleeping between polls, 32 ns to 2 us,
- * and a suspend-time hint on the poll were both measured on the stencil kernel, whose DMA warps
- * wait most of the time, also with the GPU at its power cap: no gain from the first, a 1 % loss
- * from the second.) */
-inline __device__ __noinline__ void wait_slow(uint32_t bar, uint32_t parity, unsigned int code) {
+ * or as soon as any earlier wait of the grid has given up. Returns whether the barrier was
+ * passed. (Sleeping between polls, 32 ns to 2 us, and a suspend-time hint on the poll were both
+ * measured on the stencil kernel, whose DMA warps wait most of the time, also with the GPU at its
+ * power cap: no gain from the first, a 1 % loss from the second.)
+ * A thread that gives up first sleeps for a few microseconds: copies that other threads issued
+ * just before the failure are still on their way into this CTA's shared memory, and a thread
+ * that ran on to the end of the kernel at once could take the CTA away from under them. */
+inline __device__ __noinline__ bool wait_slow(uint32_t bar, uint32_t parity, unsigned int code) {
   const long long t0 = clock64();
   unsigned int polls = 0;
   while (!ptx::mbar_try_wait(bar, parity)) {
     ++polls;
     if (polls == 16 || (polls & 1023u) == 0) {
-      if (*reinterpret_cast<volatile unsigned int *>(&g_status_word) != 0) return;
-      if (clock64() - t0 > (long long)CUDADMA_WAIT_LIMIT_CYCLES) {
-        atomicCAS(&g_status_word, 0u, code);
-        return;
-      }
+      const bool lost = *reinterpret_cast<volatile unsigned int *>(&g_status_word) != 0;
+      if (!lost && clock64() - t0 <= (long long)CUDADMA_WAIT_LIMIT_CYCLES) continue;
+      if (!lost) atomicCAS(&g_status_word, 0u, code);
+      __nanosleep(4000);
+      return false;
     }
   }
+  return true;
 }
-__device__ __forceinline__ void bounded_wait(uint32_t bar, uint32_t parity, unsigned int code) {
-  if (!ptx::mbar_try_wait(bar, parity)) wait_slow(bar, parity, code);
+__device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, unsigned int code) {
+  return ptx::mbar_try_wait(bar, parity) || wait_slow(bar, parity, code);
 }
 
 template <int UNIT> struct unit_type;
@@ -469,7 +473,8 @@ class CudaDMA {
         m_code(0x80000000u | ((unsigned)dmaID << 8)),
         m_async_proxy(async_proxy),
         m_count((uint32_t)(num_dma_threads + num_compute_threads)),
-        m_phase(0) {
+        m_phase(0),
+        m_gave_up(false) {
     if (do_sync && (dmaID < 0 || dmaID >= CUDADMA_MAX_IDS)) /* barrier_addr() wraps the id around; say so */
       atomicCAS(&cudadma_b200::g_status_word, 0u, 0x8000D000u | ((unsigned)dmaID & 0xFFu));
     if (do_sync && !m_named) {
@@ -504,19 +509,23 @@ class CudaDMA {
     m_phase ^= 1u;
   }
   __device__ __forceinline__ bool owns_this_thread(void) const { return m_is_dma_thread; }
-  /* DMA threads: block until the compute threads have released the buffer */
+  /* DMA threads: block until the compute threads have released the buffer. When the wait gives up
+   * (or the grid has failed already) the object issues no further asynchronous copies: nothing may
+   * still be on its way into shared memory when the kernel winds down with its error status. */
   __device__ __forceinline__ void wait_for_dma_start(void) const {
     if (m_named) { cudadma_b200::ptx::named_sync(m_bar_empty, m_count); return; }
-    cudadma_b200::detail::bounded_wait(m_bar_empty, m_phase, m_code | 1u);
+    if (!cudadma_b200::detail::bounded_wait(m_bar_empty, m_phase, m_code | 1u)) m_gave_up = true;
     m_phase ^= 1u;
     if (m_async_proxy) cudadma_b200::ptx::fence_proxy_async();
   }
   /* the same wait for DMA threads that will fill the buffer with ordinary stores: no proxy fence */
   __device__ __forceinline__ void wait_for_dma_start_for_stores(void) const {
     if (m_named) { cudadma_b200::ptx::named_sync(m_bar_empty, m_count); return; }
-    cudadma_b200::detail::bounded_wait(m_bar_empty, m_phase, m_code | 1u);
+    if (!cudadma_b200::detail::bounded_wait(m_bar_empty, m_phase, m_code | 1u)) m_gave_up = true;
     m_phase ^= 1u;
   }
+  /* Extension: true once a wait of this thread on this object has given up (see wait_for_dma_start) */
+  __device__ __forceinline__ bool gave_up(void) const { return m_gave_up; }
   /* DMA threads: this thread's share of the transfer is complete (or tracked by the barrier) */
   __device__ __forceinline__ void finish_async_dma(void) const {
     if (m_named) { cudadma_b200::ptx::named_arrive(m_bar_full, m_count); return; }
@@ -534,6 +543,7 @@ class CudaDMA {
   const bool m_async_proxy;
   const uint32_t m_count;     /* threads of both sides together */
   mutable uint32_t m_phase; /* parity this thread waits for next (empty for DMA threads, full for compute) */
+  mutable bool m_gave_up;   /* a wait for the buffer gave up: no asynchronous copy is issued any more */
 };
 
 namespace cudadma_b200 {
@@ -916,8 +926,8 @@ class CudaDMASequential : public CudaDMA {
     }
     if (DO_SYNC) wait_for_dma_start();
     else if (!m_is_dma_thread) return;
-    const int pending = issue_contiguous<DO_SYNC, LQ>(m_src, static_cast<char *>(dst), m_bytes, m_dma_tid,
-                                                      m_num_dma_threads, m_bar_full);
+    const int pending = m_gave_up ? 0 : issue_contiguous<DO_SYNC, LQ>(m_src, static_cast<char *>(dst), m_bytes, m_dma_tid,
+                                                                      m_num_dma_threads, m_bar_full);
     complete<DO_SYNC>(pending, m_bar_full);
   }
   const int m_bytes;
@@ -1052,7 +1062,7 @@ class CudaDMAStrided : public CudaDMA {
     static_assert(!STAGED, "this instantiation is small enough to be staged through registers and has no mbarrier "
                            "for a tensor-map transfer to count on; build with -DCUDADMA_NO_REGISTER_STAGING");
     wait_for_dma_start();
-    if (m_dma_tid == 0) {
+    if (m_dma_tid == 0 && !m_gave_up) {
       cudadma_b200::ptx::mbar_expect_tx(m_bar_full, box_bytes * (uint32_t)nboxes);
       const uint32_t d = cudadma_b200::ptx::smem_u32(dst);
       for (int b = 0; b < nboxes; ++b)
@@ -1123,8 +1133,10 @@ class CudaDMAStrided : public CudaDMA {
     }
     if (DO_SYNC) wait_for_dma_start();
     else if (!m_is_dma_thread) return;
-    int pending;
-    if (m_src_stride == m_bytes && m_dst_stride == m_bytes) {
+    int pending = 0;
+    if (m_gave_up) {
+      /* nothing is issued after a failed wait */
+    } else if (m_src_stride == m_bytes && m_dst_stride == m_bytes) {
       pending = issue_contiguous<DO_SYNC, LQ>(m_src, static_cast<char *>(dst), m_bytes * m_rows, m_dma_tid,
                                               m_num_dma_threads, m_bar_full);
     } else {
@@ -1243,7 +1255,7 @@ class CudaDMAIndirect : public CudaDMA {
     wait_for_dma_start();
     if (!MAY_BULK) cudadma_b200::ptx::fence_proxy_async();
     const int groups = m_rows >> 2;
-    const int mine = (groups > m_dma_tid) ? (groups - m_dma_tid + m_num_dma_threads - 1) / m_num_dma_threads : 0;
+    const int mine = (groups > m_dma_tid && !m_gave_up) ? (groups - m_dma_tid + m_num_dma_threads - 1) / m_num_dma_threads : 0;
     if (mine > 0) {
       cudadma_b200::ptx::mbar_expect_tx(m_bar_full, (uint32_t)mine * 4u * (uint32_t)m_bytes);
       const uint32_t d = cudadma_b200::ptx::smem_u32(dst);
@@ -1267,7 +1279,7 @@ class CudaDMAIndirect : public CudaDMA {
     if (!MAY_BULK) cudadma_b200::ptx::fence_proxy_async(); /* the rows were written by ordinary or cp.async stores */
     const int groups = m_rows >> 2;
     const uint32_t s0 = cudadma_b200::ptx::smem_u32(src);
-    for (int g = m_dma_tid; g < groups; g += m_num_dma_threads) {
+    for (int g = m_gave_up ? groups : m_dma_tid; g < groups; g += m_num_dma_threads) {
       const int4 ix = __ldg(reinterpret_cast<const int4 *>(index_ptr) + g);
       cudadma_b200::ptx::tensor_scatter4(map, 0, ix.x, ix.y, ix.z, ix.w, s0 + (uint32_t)g * 4u * (uint32_t)m_bytes);
     }
@@ -1294,8 +1306,10 @@ class CudaDMAIndirect : public CudaDMA {
     else if (!m_is_dma_thread) return;
     const unsigned long long mask = addr_bits(m_src) | addr_bits(dst) | (unsigned long long)m_bytes |
                                     (unsigned long long)m_pitch;
-    int pending;
-    if (GATHER) {
+    int pending = 0;
+    if (m_gave_up) {
+      /* nothing is issued after a failed wait */
+    } else if (GATHER) {
       GatherRows a = {m_src, static_cast<char *>(dst), m_index, m_bytes, m_pitch};
       pending = issue_rows<DO_SYNC, LQ>(a, m_rows, m_bytes, mask, m_dma_tid, m_num_dma_threads, m_bar_full);
     } else {
@@ -1370,7 +1384,7 @@ class CudaDMAHalo : public CudaDMA {
 
   __device__ __forceinline__ void execute_dma(const void *__restrict__ src_origin, void *__restrict__ dst_origin) const {
     wait_for_dma_start();
-    const int pending = issue_ring<true>(src_origin, dst_origin);
+    const int pending = m_gave_up ? 0 : issue_ring<true>(src_origin, dst_origin);
     cudadma_b200::detail::complete<true>(pending, m_bar_full);
   }
   /* same copy without either barrier; the data is in place when the call returns */
@@ -1386,7 +1400,7 @@ class CudaDMAHalo : public CudaDMA {
   __device__ __forceinline__ void execute_dma_tile(const CUtensorMap *map, const int x0, const int y0, const int z,
                                                    void *tile) const {
     wait_for_dma_start();
-    if (m_dma_tid == 0) {
+    if (m_dma_tid == 0 && !m_gave_up) {
       cudadma_b200::ptx::mbar_expect_tx(
           m_bar_full, (uint32_t)((m_dimx + 2 * RADIUS) * (m_dimy + 2 * RADIUS)) * (uint32_t)sizeof(ELMT_TYPE));
       cudadma_b200::ptx::tensor_g2s_3d(cudadma_b200::ptx::smem_u32(tile), map, x0 - RADIUS, y0 - RADIUS, z,

@@ -173,6 +173,10 @@ int cudadma_slab_export(void *slab, void *handles);
 int cudadma_slab_connect(void *slab, const void *lower_handles, const void *upper_handles);
 int cudadma_slab_connect_local(void *slab, void *lower_slab, void *upper_slab);
 int cudadma_slab_set_wait_limit(void *slab, long long sm_cycles);
+/* Tuning: depth of the two boundary runs of a step, which are dispatched first so that the step
+ * count can go out early (default 32; 0 = equal runs, the count then goes out at the end of the
+ * step; at least 8 otherwise). Slabs shallower than two such runs plus one plane use equal runs. */
+int cudadma_slab_set_edge_planes(void *slab, int planes);
 int cudadma_slab_buffer(void *slab, int which, float **ptr);
 int cudadma_slab_step(void *slab, const float coeff[5], void *stream);
 int cudadma_slab_status(void *slab, void *stream);

@@ -65,13 +65,15 @@ def test_multi_rejects_bad_arguments():
     assert lib.cudadma_stencil25_multi_destroy(None) == 0
 
 
-def test_a_neighbour_that_never_arrives_ends_the_step_with_a_status():
+@pytest.mark.parametrize("nx,ny,nzl", [(64, 32, 24), (512, 512, 100)])
+def test_a_neighbour_that_never_arrives_ends_the_step_with_a_status(nx, ny, nzl):
     """Two slabs joined in one process; only the lower one ever steps. Its second step needs the
     upper one to have finished a step, which never happens: the boundary CTAs' wait (limit set
     to a few milliseconds here) runs out, nothing is stored into the upper slab's ghost planes,
     the step count is not published, the status call reports it, later steps are refused, and the
-    GPU goes on working."""
-    nx, ny, nzl = 64, 32, 24
+    GPU goes on working. The larger case has 512 boundary CTAs in two 32-plane runs; their DMA
+    warps leave without loading anything and their compute threads run through their planes with
+    every wait giving up at once."""
     field = oracle.fill_uniform(nx * ny * nzl, 0xC4, 0.0, 1.0)
     lower, upper = cd.Slab(nx, ny, nzl, False, True), cd.Slab(nx, ny, nzl, True, False)
     try:
