@@ -230,11 +230,22 @@ __device__ __forceinline__ void compute_side(RING &ring, const unsigned char *sm
       if (!pb || !sound) continue;
       const int zb = side ? (peer.hi_begin > z0 ? peer.hi_begin : z0) : z0;
       const int ze = side ? z0 + depth : (peer.lo_end < z0 + depth ? peer.lo_end : z0 + depth);
+      /* at most R planes, two at a time: the loads of a pair first, then its stores, so that the
+       * read-backs (L2 hits) overlap instead of each plane's stores waiting for that plane's loads
+       * (all four planes at once made the compiler spill inside the kernel) */
 #pragma unroll 1
-      for (int z = zb; z < ze; ++z) {
+      for (int z = zb; z < ze; z += 2) {
         const long long plane = (long long)(z - z0) * pz;
-        if (row0_ok) *reinterpret_cast<float4 *>(pb + cell0 + plane) = *reinterpret_cast<const float4 *>(o + plane);
-        if (row1_ok) *reinterpret_cast<float4 *>(pb + cell0 + plane + py) = *reinterpret_cast<const float4 *>(o + plane + py);
+        const bool two = z + 1 < ze;
+        float4 a0, a1, b0, b1;
+        if (row0_ok) a0 = *reinterpret_cast<const float4 *>(o + plane);
+        if (row1_ok) a1 = *reinterpret_cast<const float4 *>(o + plane + py);
+        if (two && row0_ok) b0 = *reinterpret_cast<const float4 *>(o + plane + pz);
+        if (two && row1_ok) b1 = *reinterpret_cast<const float4 *>(o + plane + pz + py);
+        if (row0_ok) *reinterpret_cast<float4 *>(pb + cell0 + plane) = a0;
+        if (row1_ok) *reinterpret_cast<float4 *>(pb + cell0 + plane + py) = a1;
+        if (two && row0_ok) *reinterpret_cast<float4 *>(pb + cell0 + plane + pz) = b0;
+        if (two && row1_ok) *reinterpret_cast<float4 *>(pb + cell0 + plane + pz + py) = b1;
       }
     }
     if (sync.ticket) {
