@@ -37,6 +37,7 @@ BYTES_PER_POINT = 8                    # one fp32 read + one fp32 write per poin
 STENCIL_DRAM_BYTES_PER_POINT = 1046.4e6 / 512 ** 3
 L2_FLUSH_BYTES = 256 << 20
 EXCHANGE = "p2p"                       # halo exchange of this repository's arm at N > 1 (--exchange)
+P2P_SIGNAL = None                      # who publishes a rank's step count in that exchange (--p2p-signal; None: library default)
 
 
 def measured_peaks():
@@ -576,7 +577,7 @@ def make_stencil(impl, nz_global, weights=None):
     import cudadma_b200 as cd
     from cudadma_b200.sharded import ShardedStencil
     if impl == "ours":
-        return ShardedStencil(NX, NY, nz_global, exchange=EXCHANGE, weights=weights)
+        return ShardedStencil(NX, NY, nz_global, exchange=EXCHANGE, weights=weights, p2p_signal=P2P_SIGNAL)
     if "best" not in _REFERENCE_STENCIL:
         # which form of the reference-class stencil is fastest here: tried once, on a 1024 x 1024 x 64 padded slab
         pad = (NX + 8) * (NY + 8) * (64 + 8)
@@ -792,8 +793,10 @@ def run_stencil_job(impl, args, rank, world, local, peak, peak_kind):
                    "slab_balance": ({"rates_gpts": rates, "note": "slabs cut in proportion to each GPU's stencil rate, "
                                      "measured alone on a 256-plane field just before"} if rates else "equal slabs"),
                    "exchange": ("none" if world == 1 else "torch.distributed send/recv (NCCL)" if (impl != "ours" or EXCHANGE == "nccl")
-                                else "one launch per step: boundary CTAs wait for the neighbours' step count, store their planes into "
-                                     "the neighbours' ghost planes over NVLink (CUDA IPC) and publish this rank's count"),
+                                else "boundary CTAs wait for the neighbours' step count and store their planes into the neighbours' "
+                                     "ghost planes over NVLink (CUDA IPC); the step count is published by " +
+                                     ("the kernel's last boundary CTA (one launch per step)" if P2P_SIGNAL == "fused"
+                                      else "a one-thread launch behind the kernel")),
                    "l2": "inputs larger than L2 (%.1f GiB per array per GPU)" % (slab_pts * 4 / 2**30),
                    "synthetic_for": "uniform[0,1) field, element i = u(splitmix64(0xC4 + i)), the same global field at every N"},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1),
@@ -895,13 +898,17 @@ def main():
                     help="equal slabs on every GPU instead of slabs in proportion to the GPUs' measured rates")
     ap.add_argument("--exchange", default="p2p", choices=("p2p", "nccl"),
                     help="halo exchange at N > 1: peer-to-peer stores from the boundary kernel, or NCCL send/recv")
+    ap.add_argument("--p2p-signal", default=None, choices=("trailing", "fused"),
+                    help="p2p exchange: the step count is published by a one-thread launch behind the step's kernel "
+                         "(trailing, the library's default) or by the kernel's last boundary CTA (fused, one launch per step)")
     ap.add_argument("--profile-case", default=None,
                     help="run only a small case of one kernel (stencil_512, stencil_c5, sequential, strided, indirect, indirect_tma, "
                          "indirect_scatter4, indirect_portable) "
                          "--steps times, for a profiler capture")
     args = ap.parse_args()
-    global EXCHANGE
+    global EXCHANGE, P2P_SIGNAL
     EXCHANGE = args.exchange
+    P2P_SIGNAL = args.p2p_signal
     peak, peak_kind = measured_peaks()
     if args.profile_case:
         if not torch.cuda.is_available():
@@ -942,12 +949,13 @@ def main():
     del st
     torch.cuda.empty_cache()
     if impl == "ours":
-        # launches of this library per timed step: one kernel (p2p folds the neighbour handshake into it);
-        # the nccl form makes three (two boundary runs and the interior)
+        # launches of this library per timed step: one kernel at one GPU; p2p: the kernel and the one-thread launch
+        # that publishes the step count (fused: the kernel alone); the nccl form: two boundary runs and the interior
         if world > 1:
             line["config"]["host_threads"] = ("each rank bound to the %d cores NVML lists for its GPU" % len(HOST_CORES)) if HOST_CORES \
                 else "not bound (no NVML core list)"
-        line["gpu_launches"] = args.steps * (1 if (world == 1 or EXCHANGE == "p2p") else 3)
+        line["gpu_launches"] = args.steps * (1 if (world == 1 or (EXCHANGE == "p2p" and P2P_SIGNAL == "fused")) else
+                                             2 if EXCHANGE == "p2p" else 3)
         line["launches_total_this_process"] = cd.launch_count() - before
     else:
         line["impl"] = "reference"

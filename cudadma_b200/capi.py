@@ -61,6 +61,7 @@ SYMBOLS = [
     ("cudadma_slab_connect_local", _c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p]),
     ("cudadma_slab_set_wait_limit", _c.c_int, [_c.c_void_p, _c.c_longlong]),
     ("cudadma_slab_set_edge_planes", _c.c_int, [_c.c_void_p, _c.c_int]),
+    ("cudadma_slab_set_signal_mode", _c.c_int, [_c.c_void_p, _c.c_int]),
     ("cudadma_slab_buffer", _c.c_int, [_c.c_void_p, _c.c_int, _c.POINTER(_c.c_void_p)]),
     ("cudadma_slab_step", _c.c_int, [_c.c_void_p, _c.POINTER(_c.c_float), _c.c_void_p]),
     ("cudadma_slab_status", _c.c_int, [_c.c_void_p, _c.c_void_p]),
@@ -318,6 +319,12 @@ class Slab:
     def set_wait_limit(self, sm_cycles):
         _check("cudadma_slab_set_wait_limit", lib().cudadma_slab_set_wait_limit(self._h, int(sm_cycles)))
 
+    def set_signal_mode(self, mode):
+        """mode: "trailing" (a one-thread launch behind the step publishes the step count) or "fused"
+        (one launch per step; the last boundary CTA publishes)."""
+        _check("cudadma_slab_set_signal_mode",
+               lib().cudadma_slab_set_signal_mode(self._h, {"trailing": 0, "fused": 1}[mode]))
+
     def set_edge_planes(self, planes):
         _check("cudadma_slab_set_edge_planes", lib().cudadma_slab_set_edge_planes(self._h, int(planes)))
 
@@ -360,12 +367,18 @@ class MultiStencil:
     per entry of `devices` (default: GPUs 0 .. n_gpus - 1; repeated entries put several slabs on
     one GPU), host fields in, host fields out."""
 
-    def __init__(self, n_gpus, nx, ny, nz, devices=None):
+    def __init__(self, n_gpus, nx, ny, nz, devices=None, signal_mode=None):
         self.n, self.nx, self.ny, self.nz = n_gpus, nx, ny, nz
         h = ctypes.c_void_p()
         dev = None if devices is None else (ctypes.c_int * n_gpus)(*[int(d) for d in devices])
         _check("cudadma_stencil25_multi_create", lib().cudadma_stencil25_multi_create(ctypes.byref(h), n_gpus, dev, nx, ny, nz))
         self._h = h
+        if signal_mode is not None:   # "trailing" or "fused", see Slab.set_signal_mode
+            for r in range(n_gpus):
+                s = ctypes.c_void_p()
+                _check("cudadma_stencil25_multi_slab", lib().cudadma_stencil25_multi_slab(self._h, r, ctypes.byref(s), None, None))
+                _check("cudadma_slab_set_signal_mode",
+                       lib().cudadma_slab_set_signal_mode(s, {"trailing": 0, "fused": 1}[signal_mode]))
 
     def load(self, h_field):
         _check("cudadma_stencil25_multi_load", lib().cudadma_stencil25_multi_load(self._h, _ptr(h_field)))

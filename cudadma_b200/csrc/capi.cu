@@ -309,7 +309,7 @@ int launch_stencil_native(float *out, const stencil25::Peers &peer, stencil25::S
   if (plan.zc > 65535 || tiles_y > 65535) return CUDADMA_ERR_ARG;
   if (sync.ticket) {
     sync.boundary_ctas = boundary_ctas(plan, tiles, peer, z_begin, z_end);
-    if (sync.boundary_ctas == 0) sync = NO_SYNC;
+    if (sync.boundary_ctas == 0) sync.ticket = nullptr;
   }
   const CUtensorMap *map = nullptr;
   if (int r = stencil_map(&map, in, nx, ny, nz)) return r;
@@ -766,6 +766,23 @@ struct SlabHandles {            /* what a rank publishes to its z-neighbours */
 
 constexpr long long SLAB_WAIT_LIMIT_CYCLES = 1ll << 32; /* about two seconds */
 constexpr int SLAB_EDGE_PLANES = 32;                    /* depth of the two boundary runs of a slab step */
+#ifndef CUDADMA_SLAB_SIGNAL_DEFAULT
+#define CUDADMA_SLAB_SIGNAL_DEFAULT CUDADMA_SLAB_SIGNAL_TRAILING
+#endif
+
+/* CUDADMA_SLAB_SIGNAL_TRAILING: one thread, launched behind the step's kernel, publishes the step
+ * count. Everything the kernel wrote -- its own planes and the copies stored into the neighbours'
+ * ghost planes -- is complete when this launch starts; the system-scope fence and release stores
+ * order it before the flags. After a wait of the step gave up nothing is published. */
+__global__ void slab_signal_kernel(unsigned int *peer_lo, unsigned int *peer_hi, const unsigned int value,
+                                   unsigned int *failed) {
+  const unsigned int w = *reinterpret_cast<volatile unsigned int *>(&cudadma_b200::g_status_word);
+  if (w != 0u) { atomicCAS(failed, 0u, w); return; }
+  if (*reinterpret_cast<volatile unsigned int *>(failed) != 0u) return;
+  __threadfence_system();
+  if (peer_lo) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peer_lo), "r"(value) : "memory");
+  if (peer_hi) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peer_hi), "r"(value) : "memory");
+}
 
 struct Slab {
   int device;
@@ -782,6 +799,7 @@ struct Slab {
   unsigned int step;            /* steps finished */
   long long wait_limit;         /* SM cycles a boundary CTA waits for a neighbour */
   int edge;                     /* depth of the two boundary runs of a step (0: equal runs) */
+  int signal_mode;              /* CUDADMA_SLAB_SIGNAL_*: who publishes the step count */
   bool failed;                  /* a failure word was read back: no further steps */
 };
 
@@ -799,6 +817,7 @@ int cudadma_slab_create(void **out, int nx, int ny, int nzl, int has_lower, int 
   sl->has_lo = has_lower != 0; sl->has_hi = has_upper != 0;
   sl->wait_limit = SLAB_WAIT_LIMIT_CYCLES;
   sl->edge = SLAB_EDGE_PLANES;
+  sl->signal_mode = CUDADMA_SLAB_SIGNAL_DEFAULT;
   const size_t bytes = (size_t)nx * ny * (nzl + 8) * sizeof(float);
   cudaError_t e = cudaMalloc(&sl->buf[0], bytes);
   if (e == cudaSuccess) e = cudaMalloc(&sl->buf[1], bytes);
@@ -903,6 +922,13 @@ int cudadma_slab_set_edge_planes(void *slab, int planes) {
   return CUDADMA_OK;
 }
 
+int cudadma_slab_set_signal_mode(void *slab, int mode) {
+  Slab *sl = static_cast<Slab *>(slab);
+  if (!sl || (mode != CUDADMA_SLAB_SIGNAL_TRAILING && mode != CUDADMA_SLAB_SIGNAL_FUSED)) return CUDADMA_ERR_ARG;
+  sl->signal_mode = mode;
+  return CUDADMA_OK;
+}
+
 int cudadma_slab_buffer(void *slab, int which, float **ptr) {
   Slab *sl = static_cast<Slab *>(slab);
   if (!sl || !ptr || which < 0 || which > 1) return CUDADMA_ERR_ARG;
@@ -929,19 +955,26 @@ int cudadma_slab_step(void *slab, const float coeff[5], void *stream) {
   stencil25::Sync sync = NO_SYNC;
   if (sl->has_lo) { peer.lo = sl->lo_buf[sl->cur ^ 1] + (long long)sl->nzl_lo * pz; peer.lo_end = first + 4; }
   if (sl->has_hi) { peer.hi = sl->hi_buf[sl->cur ^ 1] - (long long)nzl * pz; peer.hi_begin = last - 4; }
-  if (sl->has_lo || sl->has_hi) {
+  const bool sharded = sl->has_lo || sl->has_hi;
+  const bool fused = sl->signal_mode == CUDADMA_SLAB_SIGNAL_FUSED;
+  if (sharded) {
     sync.wait_lo = sl->has_lo ? sl->flags + 0 : nullptr;
     sync.wait_hi = sl->has_hi ? sl->flags + 1 : nullptr;
     sync.signal_lo = sl->has_lo ? sl->lo_flags + 1 : nullptr;
     sync.signal_hi = sl->has_hi ? sl->hi_flags + 0 : nullptr;
-    sync.ticket = sl->flags + 2;
+    sync.ticket = fused ? sl->flags + 2 : nullptr;
     sync.failed = sl->flags + 3;
     sync.step = sl->step;
     sync.wait_limit = sl->wait_limit;
   }
+  /* boundary runs of their own only pay where they let the step count go out early */
   if (int r = launch_stencil_native(nxt, peer, sync, cur, nx, ny, nzt, first, last, coeff, 0,
-                                    (sl->has_lo || sl->has_hi) ? sl->edge : 0, s))
+                                    (sharded && fused) ? sl->edge : 0, s))
     return r;
+  if (sharded && !fused) {
+    slab_signal_kernel<<<1, 1, 0, s>>>(sync.signal_lo, sync.signal_hi, sl->step + 1, sl->flags + 3);
+    if (int r = launched()) return r;
+  }
   sl->cur ^= 1;
   sl->step += 1;
   return CUDADMA_OK;

@@ -63,7 +63,8 @@ struct Peers {
  * at a shared boundary take part: they read the ghost planes a neighbour filled during its last
  * step and they store into the neighbour's ghost planes, so before their first load they wait
  * (bounded) until that neighbour's flag has reached `step`, and the last of them to retire
- * (ticket counts them, `boundary_ctas` in all) publishes step + 1. The wait gives up after
+ * (ticket counts them, `boundary_ctas` in all) publishes step + 1 (with a null ticket nobody in
+ * the launch publishes: the caller does it with a launch of its own behind this one). The wait gives up after
  * `wait_limit` SM cycles: it then records a code in the status word, nothing more is stored into a
  * neighbour and the step count is not published, so the neighbours' own waits run out too instead
  * of taking over a wrong plane. */
@@ -344,14 +345,18 @@ tensor_kernel(const __grid_constant__ CUtensorMap in_map, float *__restrict__ ou
   /* CTAs whose planes reach into a pushed range are the ones that touch a shared boundary */
   const bool at_lo = peer.lo && z0 < peer.lo_end, at_hi = peer.hi && z0 + depth > peer.hi_begin;
   if (ring.stage[0].owns_this_thread()) {
-    /* A neighbour that did not arrive: nothing is loaded at all, so nothing can still be on its way
+    /* The ghost planes of the lower neighbour are the first planes this CTA loads, those of the upper
+     * neighbour the last four: each wait comes directly before the first load that needs it. A
+     * neighbour that did not arrive: no further plane is loaded, so nothing can still be on its way
      * into shared memory when this CTA's compute threads, whose own waits now give up at once,
      * have run through their planes and the CTA retires. */
-    if ((at_lo || at_hi) && sync.ticket && !wait_for_neighbours(sync, at_lo, at_hi)) return;
+    if (at_lo && sync.wait_lo && !wait_for_neighbours(sync, true, false)) return;
+    const int first_upper_ghost = (at_hi && sync.wait_hi) ? depth + R : nplanes;
     for (int k0 = 0;; k0 += STAGES) {
 #pragma unroll
       for (int s = 0; s < STAGES; ++s) {
         if (k0 + s >= nplanes) return;
+        if (k0 + s == first_upper_ghost && !wait_for_neighbours(sync, false, true)) return;
         ring.stage[s].execute_dma_tile(&in_map, x0, y0, z0 - R + k0 + s, smem + s * PLANE_BYTES);
       }
     }

@@ -15,12 +15,13 @@ One step, exchange = "nccl":
      send/recv: NCCL over NVLink on GPUs) on a side stream;
   3. the remaining interior planes are computed meanwhile on the main stream;
   4. the main stream joins the exchange, buffers swap.
-One step, exchange = "p2p" (CUDA devices only): ONE kernel launch. Its CTAs at
-a shared boundary wait (bounded) for the neighbour's step count, all owned
-planes are computed, the first and last four stored a second time, into the
-neighbours' ghost planes over NVLink (the arrays are shared between the
-processes with CUDA IPC), and the last boundary CTA publishes this rank's step
-count while the interior is still running; see cudadma_slab_step in
+One step, exchange = "p2p" (CUDA devices only): the kernel's CTAs at a shared
+boundary wait (bounded) for the neighbour's step count, all owned planes are
+computed, the first and last four stored a second time, into the neighbours'
+ghost planes over NVLink (the arrays are shared between the processes with
+CUDA IPC), and this rank's step count is published by a one-thread launch
+behind the kernel (or, p2p_signal="fused", by the kernel's last boundary CTA
+while the interior is still running); see cudadma_slab_step in
 include/cudadma_b200.h. No collective library on the step.
 Every plane is computed by the same kernel with the same arithmetic whatever
 the sharding, so an N-rank run reproduces the 1-rank field bit for bit.
@@ -109,13 +110,16 @@ class ShardedStencil:
     CPU ranks pass their own step function)."""
 
     def __init__(self, nx, ny, nz, coeff=None, device=None, group=None, step_fn=None, pad_xy=0, exchange="nccl",
-                 weights=None, exchange_timeout=None):
+                 weights=None, exchange_timeout=None, p2p_signal=None):
         """pad_xy: zero cells kept around every plane in x and y (0 for the tensor-map kernel, which
         needs no border; 4 for kernels that read a padded array). The step function sees the padded
         planes: nx + 2 * pad_xy by ny + 2 * pad_xy.
         weights: relative speed of every rank (same list on all ranks); slabs are cut in proportion,
         so that ranks which step in lockstep finish a step together even when their GPUs do not run
         equally fast (power-capped parts differ by several per cent). None = equal slabs.
+        p2p_signal: who publishes a rank's step count in the "p2p" exchange: "trailing" (a one-thread
+        launch behind the step's kernel) or "fused" (the step is one launch; its last boundary CTA
+        publishes); None = the library's default. The same on every rank.
         exchange_timeout: seconds a rank waits on the host for its neighbours' planes before step()
         raises ExchangeError (ranks on CPU). On CUDA devices nothing waits on the host during a
         step: a lost neighbour ends the "nccl" exchange through the process group's own timeout,
@@ -153,6 +157,8 @@ class ShardedStencil:
             if not self.on_cuda or step_fn is not _cuda_step or pad_xy != 0:
                 raise ValueError("the peer-to-peer exchange belongs to the CUDA kernel of this library")
             self.slab = capi.Slab(nx, ny, self.nzl, self.rank > 0, self.rank < self.world - 1)
+            if p2p_signal is not None:
+                self.slab.set_signal_mode(p2p_signal)
             blobs = [None] * self.world
             dist.all_gather_object(blobs, self.slab.export(), group=group)
             self.slab.connect(blobs[self.rank - 1] if self.rank > 0 else None,

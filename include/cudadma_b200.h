@@ -153,14 +153,15 @@ int cudadma_stencil25_step_padded(float *out, const float *in, int nx, int ny, i
  * Slabs of one process (one per GPU, or several on one GPU) are joined with
  * cudadma_slab_connect_local instead of export / connect; it enables peer access where the
  * slabs sit on different GPUs.
- * One step is ONE kernel launch. The CTAs at a boundary shared with a neighbour first wait until
- * that neighbour has finished the previous step (a flag word it writes into this GPU's memory;
- * the wait is bounded, about two seconds unless cudadma_slab_set_wait_limit says otherwise), the
- * first and last four owned planes are stored twice, here and in the neighbour's ghost planes over
- * NVLink, and the last boundary CTA to finish publishes this rank's step count to both
- * neighbours, while the interior of the slab is still being computed. No collective library is
- * involved. has_lower / has_upper say whether a neighbour exists on that side; nzl >= 8 then.
- * When a wait runs out (a neighbour is gone or more than the limit behind), the launch records
+ * One step: the kernel's CTAs at a boundary shared with a neighbour first wait until that
+ * neighbour has finished the previous step (a flag word it writes into this GPU's memory; the
+ * wait is bounded, about two seconds unless cudadma_slab_set_wait_limit says otherwise), all owned
+ * planes are computed, the first and last four of them stored twice, here and in the neighbour's
+ * ghost planes over NVLink, and this rank's step count is published to both neighbours, either
+ * by a one-thread launch behind the kernel or from inside it (cudadma_slab_set_signal_mode). No
+ * collective library is involved. has_lower / has_upper say whether a neighbour exists on that
+ * side; nzl >= 8 then.
+ * When a wait runs out (a neighbour is gone or more than the limit behind), the step records
  * it, stores nothing more into the neighbours and does not publish its step count, so the
  * neighbours' own waits run out as well instead of taking over wrong planes; this rank's own
  * field is undefined from then on. cudadma_slab_status(slab, stream) synchronises the stream and
@@ -173,6 +174,17 @@ int cudadma_slab_export(void *slab, void *handles);
 int cudadma_slab_connect(void *slab, const void *lower_handles, const void *upper_handles);
 int cudadma_slab_connect_local(void *slab, void *lower_slab, void *upper_slab);
 int cudadma_slab_set_wait_limit(void *slab, long long sm_cycles);
+/* Who publishes a rank's step count to its neighbours.
+ * CUDADMA_SLAB_SIGNAL_TRAILING (default): a one-thread launch behind the step's kernel, so a step is
+ * two launches and the count goes out when the whole step is done.
+ * CUDADMA_SLAB_SIGNAL_FUSED: the step is ONE launch; the slab is cut so that the CTAs at its two
+ * boundaries run first, each of them makes its stores into the neighbour visible system-wide and
+ * takes a ticket, and the last one publishes while the interior is still being computed. The
+ * neighbours get half a step of slack, but every boundary CTA pays for a system-scope fence behind
+ * its remote stores: on B200 / NVLink 5 the trailing form measured faster (weak-scaling steps of
+ * 256 planes per GPU). Set the same mode on every slab of a job before its first step. */
+enum { CUDADMA_SLAB_SIGNAL_TRAILING = 0, CUDADMA_SLAB_SIGNAL_FUSED = 1 };
+int cudadma_slab_set_signal_mode(void *slab, int mode);
 /* Tuning: depth of the two boundary runs of a step, which are dispatched first so that the step
  * count can go out early (default 32; 0 = equal runs, the count then goes out at the end of the
  * step; at least 8 otherwise). Slabs shallower than two such runs plus one plane use equal runs. */

@@ -29,10 +29,11 @@ def one_gpu_field(field, nx, ny, nz, steps):
 # nz / slabs >= 96 takes the form with two 32-plane boundary runs dispatched first; below that, equal runs
 @pytest.mark.parametrize("slabs,nx,ny,nz,steps", [(2, 64, 32, 16, 3), (3, 96, 48, 61, 4), (2, 128, 64, 200, 5),
                                                   (4, 64, 64, 400, 3), (8, 32, 32, 64, 6), (2, 36, 20, 230, 2)])
-def test_slabs_of_one_process_equal_the_single_field(slabs, nx, ny, nz, steps):
+@pytest.mark.parametrize("signal_mode", ["trailing", "fused"])
+def test_slabs_of_one_process_equal_the_single_field(slabs, nx, ny, nz, steps, signal_mode):
     field = oracle.fill_uniform(nx * ny * nz, 0xC4, 0.0, 1.0)
     want = one_gpu_field(field, nx, ny, nz, steps)
-    m = cd.MultiStencil(slabs, nx, ny, nz, devices=[0] * slabs)
+    m = cd.MultiStencil(slabs, nx, ny, nz, devices=[0] * slabs, signal_mode=signal_mode)
     try:
         assert m.planes(0)[0] == 0 and m.planes(slabs - 1)[1] == nz
         m.load(field)
@@ -65,8 +66,9 @@ def test_multi_rejects_bad_arguments():
     assert lib.cudadma_stencil25_multi_destroy(None) == 0
 
 
+@pytest.mark.parametrize("signal_mode", ["trailing", "fused"])
 @pytest.mark.parametrize("nx,ny,nzl", [(64, 32, 24), (512, 512, 100)])
-def test_a_neighbour_that_never_arrives_ends_the_step_with_a_status(nx, ny, nzl):
+def test_a_neighbour_that_never_arrives_ends_the_step_with_a_status(nx, ny, nzl, signal_mode):
     """Two slabs joined in one process; only the lower one ever steps. Its second step needs the
     upper one to have finished a step, which never happens: the boundary CTAs' wait (limit set
     to a few milliseconds here) runs out, nothing is stored into the upper slab's ghost planes,
@@ -79,6 +81,8 @@ def test_a_neighbour_that_never_arrives_ends_the_step_with_a_status(nx, ny, nzl)
     try:
         lower.connect_local(None, upper)
         upper.connect_local(lower, None)
+        lower.set_signal_mode(signal_mode)
+        upper.set_signal_mode(signal_mode)
         lower.set_wait_limit(4_000_000)   # about two milliseconds of SM clocks
         lower.tensor(0).view(nzl + 8, ny, nx)[4:4 + nzl] = dev(field).view(nzl, ny, nx)
         lower.step()                       # step 0 waits for nothing: it pushes and publishes
