@@ -898,7 +898,7 @@ def main():
                     help="equal slabs on every GPU instead of slabs in proportion to the GPUs' measured rates")
     ap.add_argument("--exchange", default="p2p", choices=("p2p", "nccl"),
                     help="halo exchange at N > 1: peer-to-peer stores from the boundary kernel, or NCCL send/recv")
-    ap.add_argument("--p2p-signal", default=None, choices=("trailing", "fused"),
+    ap.add_argument("--p2p-signal", default=None, choices=("trailing", "trailing-ascending", "fused"),
                     help="p2p exchange: the step count is published by a one-thread launch behind the step's kernel "
                          "(trailing, the library's default) or by the kernel's last boundary CTA (fused, one launch per step)")
     ap.add_argument("--profile-case", default=None,

@@ -62,6 +62,7 @@ SYMBOLS = [
     ("cudadma_slab_set_wait_limit", _c.c_int, [_c.c_void_p, _c.c_longlong]),
     ("cudadma_slab_set_edge_planes", _c.c_int, [_c.c_void_p, _c.c_int]),
     ("cudadma_slab_set_signal_mode", _c.c_int, [_c.c_void_p, _c.c_int]),
+    ("cudadma_slab_set_run_order", _c.c_int, [_c.c_void_p, _c.c_int]),
     ("cudadma_slab_buffer", _c.c_int, [_c.c_void_p, _c.c_int, _c.POINTER(_c.c_void_p)]),
     ("cudadma_slab_step", _c.c_int, [_c.c_void_p, _c.POINTER(_c.c_float), _c.c_void_p]),
     ("cudadma_slab_status", _c.c_int, [_c.c_void_p, _c.c_void_p]),
@@ -290,6 +291,16 @@ def stencil25_run(a, b, nx, ny, nz, steps, coeff=None, impl="native", stream=Non
 
 # ---- slabs of the z-sharded stencil with peer-to-peer halo pushes ----
 
+SIGNAL_MODES = {"trailing": (0, 1), "trailing-ascending": (0, 0), "fused": (1, None)}
+
+
+def _set_signal_mode(handle, mode):
+    signal, highest_first = SIGNAL_MODES[mode]
+    _check("cudadma_slab_set_signal_mode", lib().cudadma_slab_set_signal_mode(handle, signal))
+    if highest_first is not None:
+        _check("cudadma_slab_set_run_order", lib().cudadma_slab_set_run_order(handle, highest_first))
+
+
 class Slab:
     """This rank's planes of a z-sharded grid, in two arrays the library allocates so that the
     z-neighbour processes can map them (CUDA IPC) and push their boundary planes into the ghost
@@ -320,10 +331,10 @@ class Slab:
         _check("cudadma_slab_set_wait_limit", lib().cudadma_slab_set_wait_limit(self._h, int(sm_cycles)))
 
     def set_signal_mode(self, mode):
-        """mode: "trailing" (a one-thread launch behind the step publishes the step count) or "fused"
-        (one launch per step; the last boundary CTA publishes)."""
-        _check("cudadma_slab_set_signal_mode",
-               lib().cudadma_slab_set_signal_mode(self._h, {"trailing": 0, "fused": 1}[mode]))
+        """mode: "trailing" (a one-thread launch behind the step publishes the step count; the runs of
+        planes are dispatched from the top down), "trailing-ascending" (the same with the runs from the
+        bottom up) or "fused" (one launch per step; the last boundary CTA publishes)."""
+        _set_signal_mode(self._h, mode)
 
     def set_edge_planes(self, planes):
         _check("cudadma_slab_set_edge_planes", lib().cudadma_slab_set_edge_planes(self._h, int(planes)))
@@ -377,8 +388,7 @@ class MultiStencil:
             for r in range(n_gpus):
                 s = ctypes.c_void_p()
                 _check("cudadma_stencil25_multi_slab", lib().cudadma_stencil25_multi_slab(self._h, r, ctypes.byref(s), None, None))
-                _check("cudadma_slab_set_signal_mode",
-                       lib().cudadma_slab_set_signal_mode(s, {"trailing": 0, "fused": 1}[signal_mode]))
+                _set_signal_mode(s, signal_mode)
 
     def load(self, h_field):
         _check("cudadma_stencil25_multi_load", lib().cudadma_stencil25_multi_load(self._h, _ptr(h_field)))

@@ -21,10 +21,14 @@
 #define SEQ_STAGES 4
 #endif
 #ifndef SEQ_CTAS_PER_SM
-#define SEQ_CTAS_PER_SM 2
+#define SEQ_CTAS_PER_SM 3
 #endif
 #ifndef SEQ_BULK_STORE
-#define SEQ_BULK_STORE true
+#define SEQ_BULK_STORE false /* register-staged loads and plain stores; true: bulk copies both ways (dma_kernels.cuh) */
+#endif
+
+#ifndef P_SEQ_BPT
+#define P_SEQ_BPT 128 /* BYTES_PER_THREAD of the portable sequential copy's objects: staged through registers, 2 % over 64 */
 #endif
 
 #ifndef TR_STAGES
@@ -245,7 +249,7 @@ struct ChunkPlan { int z_chunk, z_edge, zc; };
 ChunkPlan plan_chunks(int depth, long long tiles, int sms, int z_chunk, int z_edge) {
   ChunkPlan p;
   if (z_edge > 0 && depth < 2 * z_edge + 1) z_edge = 0;
-  const int inner = depth - 2 * z_edge;
+  const int inner = depth - 2 * (z_edge > 0 ? z_edge : 0); /* z_edge < 0: equal runs, highest first */
   if (z_chunk <= 0) {
     /* Enough CTAs for a few waves over the SMs, but runs of at least 32 planes so that the eight
      * lead-in/lead-out planes of a run stay a small share of its loads -- and of at most
@@ -574,7 +578,7 @@ int cudadma_seq_copy(void *dst, const void *src, size_t bytes, int chunk_bytes, 
       k<<<grid, SEQ_DMA_THREADS + SEQ_COMPUTE_THREADS, STAGES * 16384, s>>>(d, p, nfull);
       if (int r = launched()) return r;
     } else if (impl == CUDADMA_IMPL_PORTABLE && chunk_bytes == 16384) {
-      if (int r = portable::launch_seq_copy(d, p, nfull, sms, s)) { t_last_cuda_error = r; return CUDADMA_ERR_CUDA; }
+      if (int r = portable::launch_seq_copy<P_SEQ_BPT>(d, p, nfull, sms, s)) { t_last_cuda_error = r; return CUDADMA_ERR_CUDA; }
       ++g_launches;
     } else if (impl == CUDADMA_IMPL_NATIVE || impl == CUDADMA_IMPL_PORTABLE) {
       const long long want = 4ll * sms;
@@ -766,6 +770,9 @@ struct SlabHandles {            /* what a rank publishes to its z-neighbours */
 
 constexpr long long SLAB_WAIT_LIMIT_CYCLES = 1ll << 32; /* about two seconds */
 constexpr int SLAB_EDGE_PLANES = 32;                    /* depth of the two boundary runs of a slab step */
+#ifndef SLAB_HIGHEST_FIRST
+#define SLAB_HIGHEST_FIRST true
+#endif
 #ifndef CUDADMA_SLAB_SIGNAL_DEFAULT
 #define CUDADMA_SLAB_SIGNAL_DEFAULT CUDADMA_SLAB_SIGNAL_TRAILING
 #endif
@@ -800,6 +807,7 @@ struct Slab {
   long long wait_limit;         /* SM cycles a boundary CTA waits for a neighbour */
   int edge;                     /* depth of the two boundary runs of a step (0: equal runs) */
   int signal_mode;              /* CUDADMA_SLAB_SIGNAL_*: who publishes the step count */
+  bool highest_first;           /* trailing mode: dispatch the runs of planes from the top down */
   bool failed;                  /* a failure word was read back: no further steps */
 };
 
@@ -818,6 +826,7 @@ int cudadma_slab_create(void **out, int nx, int ny, int nzl, int has_lower, int 
   sl->wait_limit = SLAB_WAIT_LIMIT_CYCLES;
   sl->edge = SLAB_EDGE_PLANES;
   sl->signal_mode = CUDADMA_SLAB_SIGNAL_DEFAULT;
+  sl->highest_first = SLAB_HIGHEST_FIRST;
   const size_t bytes = (size_t)nx * ny * (nzl + 8) * sizeof(float);
   cudaError_t e = cudaMalloc(&sl->buf[0], bytes);
   if (e == cudaSuccess) e = cudaMalloc(&sl->buf[1], bytes);
@@ -922,6 +931,13 @@ int cudadma_slab_set_edge_planes(void *slab, int planes) {
   return CUDADMA_OK;
 }
 
+int cudadma_slab_set_run_order(void *slab, int highest_first) {
+  Slab *sl = static_cast<Slab *>(slab);
+  if (!sl || highest_first < 0 || highest_first > 1) return CUDADMA_ERR_ARG;
+  sl->highest_first = highest_first != 0;
+  return CUDADMA_OK;
+}
+
 int cudadma_slab_set_signal_mode(void *slab, int mode) {
   Slab *sl = static_cast<Slab *>(slab);
   if (!sl || (mode != CUDADMA_SLAB_SIGNAL_TRAILING && mode != CUDADMA_SLAB_SIGNAL_FUSED)) return CUDADMA_ERR_ARG;
@@ -969,7 +985,7 @@ int cudadma_slab_step(void *slab, const float coeff[5], void *stream) {
   }
   /* boundary runs of their own only pay where they let the step count go out early */
   if (int r = launch_stencil_native(nxt, peer, sync, cur, nx, ny, nzt, first, last, coeff, 0,
-                                    (sharded && fused) ? sl->edge : 0, s))
+                                    !sharded ? 0 : fused ? sl->edge : (sl->highest_first ? -1 : 0), s))
     return r;
   if (sharded && !fused) {
     slab_signal_kernel<<<1, 1, 0, s>>>(sync.signal_lo, sync.signal_hi, sl->step + 1, sl->flags + 3);

@@ -20,24 +20,45 @@ namespace kernels {
 
 /* ------------------------------------------------------------------------ */
 /* Sequential: CHUNK-byte chunks global -> shared -> global.                 */
-/* 4 DMA warps + 8 compute warps; STAGES buffers in flight per CTA.          */
+/* 4 DMA warps + 8 compute warps; STAGES buffers per CTA.                    */
 /* Chunk c of the array is handled by CTA c % gridDim.x.                     */
-/* BULK_STORE: one compute thread writes a chunk back with a bulk store;     */
-/* otherwise all compute threads copy it with 16-byte loads and stores.      */
-/* (Measured and not kept: handing a buffer back one chunk late, so that the  */
-/* storing thread waits for the read of the PREVIOUS chunk's store, 1 to 3 % */
-/* slower on 1 GiB with four to seven buffers; L2 evict-first hints on the   */
-/* loads, the stores or both, 0 to 2 % slower; 2 to 4 buffers x 2 to 4 CTAs  */
-/* per SM, and plain 16-byte stores for the write-back, all within 3 % below.)*/
+/* BULK_STORE == false (what the library launches): the DMA threads stage a  */
+/* chunk through registers (BYTES_PER_THREAD = 128: eight 16-byte loads per  */
+/* thread, issued before the thread waits for the buffer, stored into it     */
+/* after), the compute threads write it back with 16-byte loads and stores.  */
+/* BULK_STORE == true: cp.async.bulk in both directions (the DMA warps fill, */
+/* one compute thread writes a chunk back with a bulk store).                */
+/* Measured on 1 GiB, rotating (two GPUs): staged with 4 buffers x 3 CTAs per */
+/* SM 6.54 - 6.62 TB/s (a device-to-device cudaMemcpy 6.42 - 6.52, the        */
+/* reference classes 6.35 - 6.40); staged 3 x 3 6.44 - 6.49, 3 x 4 6.54,      */
+/* 2 x 4 6.16, 6 x 2 6.03; 128 or 192 compute threads 6.50, 384 6.13; 256 DMA */
+/* threads 6.41; bulk copies with 4 x 2 6.27 - 6.30. On 64 MiB arrays back to */
+/* back: staged 4 x 3 5.44 (cudaMemcpy 5.44, bulk 5.24 - 5.35, the reference  */
+/* classes 5.04 - 5.32).                                                      */
+/* Not kept for the bulk form: handing a buffer back one chunk late, so that */
+/* the storing thread waits for the read of the PREVIOUS chunk's store, 1 to */
+/* 3 % slower with four to seven buffers; L2 evict-first hints on the loads, */
+/* the stores or both, 0 to 2 % slower; 2 to 4 buffers x 2 to 4 CTAs per SM, */
+/* and plain 16-byte stores for the write-back, all within 3 % below.        */
 /* ------------------------------------------------------------------------ */
-constexpr int SEQ_DMA_THREADS = 128;
-constexpr int SEQ_COMPUTE_THREADS = 256;
+#ifndef SEQ_DMA_THREADS_N
+#define SEQ_DMA_THREADS_N 128
+#endif
+#ifndef SEQ_COMPUTE_THREADS_N
+#define SEQ_COMPUTE_THREADS_N 256
+#endif
+constexpr int SEQ_DMA_THREADS = SEQ_DMA_THREADS_N;
+constexpr int SEQ_COMPUTE_THREADS = SEQ_COMPUTE_THREADS_N;
+
+#ifndef SEQ_MIN_BLOCKS
+#define SEQ_MIN_BLOCKS 3
+#endif
 
 template <int CHUNK, int STAGES, bool BULK_STORE>
-__global__ void __launch_bounds__(SEQ_DMA_THREADS + SEQ_COMPUTE_THREADS)
+__global__ void __launch_bounds__(SEQ_DMA_THREADS + SEQ_COMPUTE_THREADS, SEQ_MIN_BLOCKS)
 seq_copy_kernel(char *__restrict__ dst, const char *__restrict__ src, const long long nchunks) {
   extern __shared__ __align__(128) unsigned char smem[];
-  typedef CudaDMASequential<true, 16, 64, CHUNK, SEQ_DMA_THREADS> Dma;
+  typedef CudaDMASequential<true, 16, BULK_STORE ? 64 : 128, CHUNK, SEQ_DMA_THREADS> Dma;
   Ring<Dma, STAGES> ring(SEQ_COMPUTE_THREADS, SEQ_COMPUTE_THREADS);
   const long long stride = gridDim.x;
 

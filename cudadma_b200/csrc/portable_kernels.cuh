@@ -190,7 +190,14 @@ stencil_kernel(float *__restrict__ out, const float *__restrict__ in, const int 
 template <int BPT = 64>
 inline int launch_seq_copy(char *dst, const char *src, long long nchunks, int sms, cudaStream_t s) {
   auto k = seq_copy_kernel<BPT>;
-  const long long want = 4ll * sms; /* 32 KiB of shared memory and 384 threads per CTA */
+  /* one resident wave of at most four CTAs per SM (32 KiB of shared memory and 384 threads per CTA;
+   * a large register budget per DMA thread leaves room for three) */
+  int fit = 0;
+  cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&fit, k, P_DMA + P_COMPUTE, 2 * P_CHUNK);
+  if (e != cudaSuccess) return (int)e;
+  if (fit < 1) fit = 1;
+  if (fit > 4) fit = 4;
+  const long long want = (long long)fit * sms;
   const int grid = (int)(nchunks < want ? nchunks : want);
   k<<<grid, P_DMA + P_COMPUTE, 2 * P_CHUNK, s>>>(dst, src, nchunks);
   return (int)cudaGetLastError();

@@ -310,6 +310,11 @@ __device__ __forceinline__ bool wait_for_neighbours(const Sync &sync, const bool
  * of a CTA are numbered kp = 0 .. depth + 7 from (first output plane - 4); output plane kp - 8 is
  * stored at step kp.
  * Runs of planes per CTA: z_edge == 0: blockIdx.z takes planes [z_begin + blockIdx.z * z_chunk, + z_chunk).
+ * z_edge < 0: the same runs, highest first (run gridDim.z - 1 - blockIdx.z). A sharded rank whose step
+ * count goes out behind the kernel uses this: the CTAs that wait for the LOWER neighbour before their
+ * first load then start in the second half of the launch, and those of the top run wait for the upper
+ * neighbour only before their last four planes, so neither wait is met at the start of the kernel
+ * and two GPUs can drift against each other by a good part of a step without either of them idling.
  * z_edge > 0 (sharded ranks): blockIdx.z == 0 takes the lowest z_edge planes, blockIdx.z == 1 the
  * highest z_edge planes, and blockIdx.z >= 2 runs of z_chunk planes of what lies between. CTAs are
  * dispatched in blockIdx order, so both boundary runs start first and the step count can go out
@@ -338,7 +343,8 @@ tensor_kernel(const __grid_constant__ CUtensorMap in_map, float *__restrict__ ou
       depth = (z_end - z_edge - z0 < z_chunk) ? (z_end - z_edge - z0) : z_chunk;
     }
   } else {
-    z0 = z_begin + blockIdx.z * z_chunk;
+    const int run = z_edge < 0 ? (int)(gridDim.z - 1 - blockIdx.z) : (int)blockIdx.z;
+    z0 = z_begin + run * z_chunk;
     depth = (z_end - z0 < z_chunk) ? (z_end - z0) : z_chunk;
   }
   const int nplanes = depth + 2 * R;

@@ -118,8 +118,9 @@ class ShardedStencil:
         so that ranks which step in lockstep finish a step together even when their GPUs do not run
         equally fast (power-capped parts differ by several per cent). None = equal slabs.
         p2p_signal: who publishes a rank's step count in the "p2p" exchange: "trailing" (a one-thread
-        launch behind the step's kernel) or "fused" (the step is one launch; its last boundary CTA
-        publishes); None = the library's default. The same on every rank.
+        launch behind the step's kernel, runs of planes dispatched from the top down),
+        "trailing-ascending" (the same, from the bottom up) or "fused" (the step is one launch; its
+        last boundary CTA publishes); None = the library's default. The same on every rank.
         exchange_timeout: seconds a rank waits on the host for its neighbours' planes before step()
         raises ExchangeError (ranks on CPU). On CUDA devices nothing waits on the host during a
         step: a lost neighbour ends the "nccl" exchange through the process group's own timeout,

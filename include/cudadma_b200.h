@@ -185,6 +185,12 @@ int cudadma_slab_set_wait_limit(void *slab, long long sm_cycles);
  * 256 planes per GPU). Set the same mode on every slab of a job before its first step. */
 enum { CUDADMA_SLAB_SIGNAL_TRAILING = 0, CUDADMA_SLAB_SIGNAL_FUSED = 1 };
 int cudadma_slab_set_signal_mode(void *slab, int mode);
+/* Trailing mode: the order in which the kernel's runs of planes are dispatched. highest_first = 1
+ * (default): from the top of the slab down. The CTAs of the top run need the upper neighbour only
+ * before their last four planes, and those of the bottom run, which need the lower neighbour before
+ * their first load, start in the second half of the launch: no CTA waits at the start of a kernel,
+ * and neighbouring GPUs may drift against each other by a good part of a step. 0: from the bottom up. */
+int cudadma_slab_set_run_order(void *slab, int highest_first);
 /* Tuning: depth of the two boundary runs of a step, which are dispatched first so that the step
  * count can go out early (default 32; 0 = equal runs, the count then goes out at the end of the
  * step; at least 8 otherwise). Slabs shallower than two such runs plus one plane use equal runs. */

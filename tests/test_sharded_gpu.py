@@ -30,8 +30,8 @@ def _worker(rank, world, port, nx, ny, nz, steps, exchange, q, weights=None, p2p
         from cudadma_b200.sharded import ShardedStencil
         from oracle import oracle
         field = oracle.fill_uniform(nx * ny * nz, 0xC4, 0.0, 1.0).reshape(nz, ny, nx)
-        if exchange == "p2p-fused":
-            exchange, p2p_signal = "p2p", "fused"
+        if exchange.startswith("p2p-"):    # "p2p-fused", "p2p-trailing-ascending"
+            exchange, p2p_signal = "p2p", exchange[4:]
         st = ShardedStencil(nx, ny, nz, exchange=exchange, weights=weights, p2p_signal=p2p_signal)
         st.load(torch.from_numpy(field[st.z_lo:st.z_hi].copy()).cuda())
         got = st.run(steps).cpu().numpy().copy()
@@ -47,7 +47,8 @@ def _worker(rank, world, port, nx, ny, nz, steps, exchange, q, weights=None, p2p
 @pytest.mark.parametrize("nz,steps,exchange,weights",
                          [(40, 3, "nccl", None), (19, 2, "nccl", None), (40, 5, "p2p", None), (17, 2, "p2p", None),
                           (48, 4, "p2p", (1.0, 1.7)), (48, 3, "nccl", (2.1, 1.0)), (230, 4, "p2p", None),
-                          (40, 5, "p2p-fused", None), (230, 4, "p2p-fused", None), (48, 4, "p2p-fused", (1.0, 1.7))])
+                          (40, 5, "p2p-fused", None), (230, 4, "p2p-fused", None), (48, 4, "p2p-fused", (1.0, 1.7)),
+                          (230, 4, "p2p-trailing-ascending", None), (600, 3, "p2p", None)])
 def test_two_gpus_equal_one_gpu(nz, steps, exchange, weights):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two CUDA devices")

@@ -29,7 +29,7 @@ def one_gpu_field(field, nx, ny, nz, steps):
 # nz / slabs >= 96 takes the form with two 32-plane boundary runs dispatched first; below that, equal runs
 @pytest.mark.parametrize("slabs,nx,ny,nz,steps", [(2, 64, 32, 16, 3), (3, 96, 48, 61, 4), (2, 128, 64, 200, 5),
                                                   (4, 64, 64, 400, 3), (8, 32, 32, 64, 6), (2, 36, 20, 230, 2)])
-@pytest.mark.parametrize("signal_mode", ["trailing", "fused"])
+@pytest.mark.parametrize("signal_mode", ["trailing", "trailing-ascending", "fused"])
 def test_slabs_of_one_process_equal_the_single_field(slabs, nx, ny, nz, steps, signal_mode):
     field = oracle.fill_uniform(nx * ny * nz, 0xC4, 0.0, 1.0)
     want = one_gpu_field(field, nx, ny, nz, steps)
@@ -66,8 +66,8 @@ def test_multi_rejects_bad_arguments():
     assert lib.cudadma_stencil25_multi_destroy(None) == 0
 
 
-@pytest.mark.parametrize("signal_mode", ["trailing", "fused"])
-@pytest.mark.parametrize("nx,ny,nzl", [(64, 32, 24), (512, 512, 100)])
+@pytest.mark.parametrize("signal_mode", ["trailing", "trailing-ascending", "fused"])
+@pytest.mark.parametrize("nx,ny,nzl", [(64, 32, 24), (512, 512, 100), (256, 256, 300)])
 def test_a_neighbour_that_never_arrives_ends_the_step_with_a_status(nx, ny, nzl, signal_mode):
     """Two slabs joined in one process; only the lower one ever steps. Its second step needs the
     upper one to have finished a step, which never happens: the boundary CTAs' wait (limit set
@@ -75,7 +75,8 @@ def test_a_neighbour_that_never_arrives_ends_the_step_with_a_status(nx, ny, nzl,
     the step count is not published, the status call reports it, later steps are refused, and the
     GPU goes on working. The larger case has 512 boundary CTAs in two 32-plane runs; their DMA
     warps leave without loading anything and their compute threads run through their planes with
-    every wait giving up at once."""
+    every wait giving up at once. The deepest case has three runs of planes per tile, so that in the
+    descending order the run that waits comes last."""
     field = oracle.fill_uniform(nx * ny * nzl, 0xC4, 0.0, 1.0)
     lower, upper = cd.Slab(nx, ny, nzl, False, True), cd.Slab(nx, ny, nzl, True, False)
     try:
