@@ -704,6 +704,11 @@ __device__ __forceinline__ void prefetch_small(const char *src, const int rows, 
  * trip to memory per link where the early loads overlap it with the consumer's work on the
  * previous buffer (the reference's saxpy example, 1 KiB per transfer: 0.39 us per iteration
  * against 0.19). All indices are compile-time, so the staging array stays in registers.
+ * A unit's offset from the base pointer is computed in 32-bit ints, as the reference's offsets
+ * are: the rows of a staged transfer must lie within 2 GiB of its base pointer. (With 64-bit
+ * offsets the compiler keeps one register pair per unit and pointer alive across the caller's
+ * loop: the reference's warp-specialised stencil examples took 72 registers against the
+ * reference header's 60 and lost a CTA per SM; with ints they take 56.)
  */
 template <int ROW_BYTES, int ROWS, int NTHREADS>
 struct StagedShape {
@@ -712,21 +717,21 @@ struct StagedShape {
   static constexpr int UNITS = NTHREADS > 0 ? (TOTAL + NTHREADS - 1) / NTHREADS : 0; /* per thread */
 };
 template <int ROW_BYTES, int ROWS, int NTHREADS, bool L2_ONLY, int N>
-__device__ __forceinline__ void staged_load(uint4 (&v)[N], const char *src, const long long src_stride, const int tid) {
+__device__ __forceinline__ void staged_load(uint4 (&v)[N], const char *src, const int src_stride, const int tid) {
   typedef StagedShape<ROW_BYTES, ROWS, NTHREADS> S;
 #pragma unroll
   for (int k = 0; k < S::UNITS; ++k) {
     const int i = tid + k * NTHREADS;
     if ((k + 1) * NTHREADS <= S::TOTAL || i < S::TOTAL) {
       const int r = i / S::UPR, c = i - r * S::UPR;
-      const uint4 *g = reinterpret_cast<const uint4 *>(src + (long long)r * src_stride + 16 * c);
+      const uint4 *g = reinterpret_cast<const uint4 *>(src + (r * src_stride + 16 * c));
       v[k] = L2_ONLY ? __ldcg(g) : *g; /* a plain load works from any address space */
     }
   }
 }
 /* direct: destination and its stride are multiples of 16 (else word by word) */
 template <int ROW_BYTES, int ROWS, int NTHREADS, int N>
-__device__ __forceinline__ void staged_store(const uint4 (&v)[N], char *dst, const long long dst_stride, const int tid,
+__device__ __forceinline__ void staged_store(const uint4 (&v)[N], char *dst, const int dst_stride, const int tid,
                                              const bool direct) {
   typedef StagedShape<ROW_BYTES, ROWS, NTHREADS> S;
 #pragma unroll
@@ -734,7 +739,7 @@ __device__ __forceinline__ void staged_store(const uint4 (&v)[N], char *dst, con
     const int i = tid + k * NTHREADS;
     if ((k + 1) * NTHREADS <= S::TOTAL || i < S::TOTAL) {
       const int r = i / S::UPR, c = i - r * S::UPR;
-      char *d = dst + (long long)r * dst_stride + 16 * c;
+      char *d = dst + (r * dst_stride + 16 * c);
       if (direct) {
         *reinterpret_cast<uint4 *>(d) = v[k];
       } else {

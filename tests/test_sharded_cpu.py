@@ -132,6 +132,8 @@ def _lost_neighbour_worker(rank, world, port, q, release):
         q.put((rank, "no error"))
     except sharded.ExchangeError as e:
         q.put((rank, "ExchangeError: %s" % e))
+    q.close()
+    q.join_thread()  # put() only hands the item to a feeder thread: let it reach the pipe before leaving
     os._exit(0)  # the group is not usable after a lost exchange; leave without its teardown
 
 
