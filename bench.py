@@ -533,6 +533,11 @@ def run_examples():
                 t[which] = min(ms, t.get(which, ms))
             out["%s_%s" % (kname, example)] = {"this_header_ms": round(t["ours"], 4), "reference_header_ms": round(t["ref"], 4),
                                                 "ratio": round(t["ref"] / t["ours"], 3)}
+            if example == "sequential" and ex.available("libv1saxpy_ours_ro.so"):
+                # the same build with -DCUDADMA_SOURCES_READ_ONLY (read-only data path for the staged loads)
+                ro = min(ex.run_saxpy(example, "ours_ro", kernel_id, x, y, 0.84018773)[1] for _ in range(2))
+                out["%s_%s" % (kname, example)].update(this_header_read_only_sources_ms=round(ro, 4),
+                                                       ratio_read_only_sources=round(t["ref"] / ro, 3))
     if ex.available("libperfseq_ours.so", "libperfseq_ref.so"):
         for kid, name in enumerate(ex.PERFSEQ_NAMES):
             g = {}
@@ -543,7 +548,7 @@ def run_examples():
                                               "ratio": round(g["ours"] / g["ref"], 3)}
     if not out:
         return {"unavailable": "oracle/_ref holds no example libraries (no reference checkout at build time)"}
-    out["slowest_ratio"] = min(v["ratio"] for v in out.values())
+    out["slowest_ratio"] = min(v["ratio"] for v in out.values())   # default builds only
     return out
 
 

@@ -716,7 +716,7 @@ struct StagedShape {
   static constexpr int TOTAL = UPR * ROWS;
   static constexpr int UNITS = NTHREADS > 0 ? (TOTAL + NTHREADS - 1) / NTHREADS : 0; /* per thread */
 };
-template <int ROW_BYTES, int ROWS, int NTHREADS, bool L2_ONLY, int N>
+template <int ROW_BYTES, int ROWS, int NTHREADS, bool L2_ONLY, bool GLOBAL_SRC, int N>
 __device__ __forceinline__ void staged_load(uint4 (&v)[N], const char *src, const int src_stride, const int tid) {
   typedef StagedShape<ROW_BYTES, ROWS, NTHREADS> S;
 #pragma unroll
@@ -725,7 +725,25 @@ __device__ __forceinline__ void staged_load(uint4 (&v)[N], const char *src, cons
     if ((k + 1) * NTHREADS <= S::TOTAL || i < S::TOTAL) {
       const int r = i / S::UPR, c = i - r * S::UPR;
       const uint4 *g = reinterpret_cast<const uint4 *>(src + (r * src_stride + 16 * c));
-      v[k] = L2_ONLY ? __ldcg(g) : *g; /* a plain load works from any address space */
+      /* Which load: an explicit cache qualifier goes to L2 (ld.global.cg), everything else is a
+       * plain load, which works from any address space.
+       * -DCUDADMA_SOURCES_READ_ONLY (a promise: the kernel never writes what its transfer objects
+       * read afterwards): global sources are read through the read-only data path (ld.global.nc),
+       * as the reference does for DMA_GLOBAL_LOAD on the architecture it was tuned for
+       * (cudaDMAv2.h:98-103). Such loads are not tied to the handshake's barriers, so the compiler
+       * moves them: in the reference's saxpy examples it starts the next transfer's loads before
+       * this one's wait (1.45 x and 1.23 x the reference header's speed instead of 0.93 x and
+       * 0.95 x), in its warp-specialised double-buffer stencil it moves them behind the wait
+       * (0.64 x instead of 1.09 x). Measure before keeping it.
+       * Also measured: ld.global.cg for every global source gives +3 % on those saxpy loops and
+       * +6 % on the portable stencil's windows, but -4 % on a streaming copy of 1 GiB. */
+      if (L2_ONLY) v[k] = __ldcg(g);
+#ifdef CUDADMA_SOURCES_READ_ONLY
+      else if (GLOBAL_SRC) v[k] = __ldg(g);
+      else v[k] = __isGlobal(g) ? __ldg(g) : *g;
+#else
+      else v[k] = *g;
+#endif
     }
   }
 }
@@ -776,9 +794,9 @@ __device__ __forceinline__ ArgList make_args(I... a) {
 
 #define CUDADMA_B200_XFER_OVERLOADS(SRC_DECL, SRC_ARGS)                                                     \
   __device__ __forceinline__ void execute_dma(SRC_DECL, void *__restrict__ dst_ptr) {                       \
-    execute_impl<true, LOAD_CACHE_ALL>(SRC_ARGS, dst_ptr);                                                  \
+    execute_impl<false, LOAD_CACHE_ALL>(SRC_ARGS, dst_ptr);                                                 \
   }                                                                                                         \
-  __device__ __forceinline__ void start_xfer_async(SRC_DECL) { start_impl<true, LOAD_CACHE_ALL>(SRC_ARGS); } \
+  __device__ __forceinline__ void start_xfer_async(SRC_DECL) { start_impl<false, LOAD_CACHE_ALL>(SRC_ARGS); } \
   __device__ __forceinline__ void wait_xfer_finish(void *__restrict__ dst_ptr) {                            \
     finish_impl<LOAD_CACHE_ALL>(dst_ptr);                                                                   \
   }                                                                                                         \
@@ -888,10 +906,10 @@ class CudaDMASequential : public CudaDMA {
     if (STAGED) {
       m_staged = m_is_dma_thread && (TRUST || (cudadma_b200::detail::addr_bits(src) & 15) == 0);
       if (m_staged)
-        cudadma_b200::detail::staged_load<STAGED ? BYTES_PER_ELMT : 16, 1, NT, GLOBAL && LQ != LOAD_CACHE_ALL>(m_stage, m_src, 0, m_dma_tid);
+        cudadma_b200::detail::staged_load<STAGED ? BYTES_PER_ELMT : 16, 1, NT, GLOBAL && LQ != LOAD_CACHE_ALL, GLOBAL>(m_stage, m_src, 0, m_dma_tid);
       return;
     }
-    if (DO_SYNC && GLOBAL) cudadma_b200::detail::prefetch_small(m_src, 1, m_bytes, 0, m_dma_tid, m_num_dma_threads);
+    if (DO_SYNC) cudadma_b200::detail::prefetch_small(m_src, 1, m_bytes, 0, m_dma_tid, m_num_dma_threads);
   }
   /* execute_dma: the whole transfer in one call. A staged object keeps the bytes in a local array
    * here, so that nothing of one transfer stays live into the next (the member array serves the
@@ -904,7 +922,7 @@ class CudaDMASequential : public CudaDMA {
       /* warp-specialised: only DMA threads call this (the reference's contract); otherwise every thread does */
       const bool early = (DO_SYNC || m_is_dma_thread) && (TRUST || (addr_bits(src) & 15) == 0);
       uint4 stage[Shape::UNITS > 0 ? Shape::UNITS : 1];
-      if (early) staged_load<STAGED ? BYTES_PER_ELMT : 16, 1, NT, GLOBAL && LQ != LOAD_CACHE_ALL>(stage, s, 0, m_dma_tid);
+      if (early) staged_load<STAGED ? BYTES_PER_ELMT : 16, 1, NT, GLOBAL && LQ != LOAD_CACHE_ALL, GLOBAL>(stage, s, 0, m_dma_tid);
       if (DO_SYNC) wait_for_dma_start_for_stores();
       else if (!m_is_dma_thread) return;
       if (early) {
@@ -1095,10 +1113,10 @@ class CudaDMAStrided : public CudaDMA {
       m_staged = m_is_dma_thread &&
                  (TRUST || ((cudadma_b200::detail::addr_bits(src) | (unsigned long long)(unsigned)m_src_stride) & 15) == 0);
       if (m_staged)
-        cudadma_b200::detail::staged_load<SB, SR, NT, GLOBAL && LQ != LOAD_CACHE_ALL>(m_stage, m_src, m_src_stride, m_dma_tid);
+        cudadma_b200::detail::staged_load<SB, SR, NT, GLOBAL && LQ != LOAD_CACHE_ALL, GLOBAL>(m_stage, m_src, m_src_stride, m_dma_tid);
       return;
     }
-    if (DO_SYNC && GLOBAL)
+    if (DO_SYNC)
       cudadma_b200::detail::prefetch_small(m_src, m_rows, m_bytes, m_src_stride, m_dma_tid, m_num_dma_threads);
   }
   /* execute_dma in one call; a staged object keeps the bytes in a local array (see CudaDMASequential) */
@@ -1110,7 +1128,7 @@ class CudaDMAStrided : public CudaDMA {
       const bool early = (DO_SYNC || m_is_dma_thread) &&
                          (TRUST || ((addr_bits(src) | (unsigned long long)(unsigned)m_src_stride) & 15) == 0);
       uint4 stage[STAGED ? Shape::UNITS : 1];
-      if (early) staged_load<SB, SR, NT, GLOBAL && LQ != LOAD_CACHE_ALL>(stage, s, m_src_stride, m_dma_tid);
+      if (early) staged_load<SB, SR, NT, GLOBAL && LQ != LOAD_CACHE_ALL, GLOBAL>(stage, s, m_src_stride, m_dma_tid);
       if (DO_SYNC) wait_for_dma_start_for_stores();
       else if (!m_is_dma_thread) return;
       const unsigned long long dmask = addr_bits(dst) | (unsigned long long)(unsigned)m_dst_stride;

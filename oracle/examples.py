@@ -51,7 +51,8 @@ def stencil_bandwidth_gbs(dims, ms):
 
 
 def run_saxpy(example, which, kernel_id, x, y, a):
-    """example: "sequential" or "strided". Returns (a * x + y as computed on the device, ms per launch)."""
+    """example: "sequential" or "strided"; which: "ours", "ref", or "ours_ro" (this repository's header with
+    -DCUDADMA_SOURCES_READ_ONLY, sequential only). Returns (a * x + y as computed on the device, ms per launch)."""
     name = "libv1saxpy_%s%s.so" % ("strided_" if example == "strided" else "", which)
     lib = ctypes.CDLL(_path(name))
     lib.v1saxpy_elements.restype = ctypes.c_longlong

@@ -110,6 +110,25 @@ def test_reference_v1_saxpy_example_runs_unchanged_on_this_header(example, kerne
     assert np.allclose(got, exact, rtol=1e-6, atol=0.0)
 
 
+@pytest.mark.parametrize("kernel_id", [0, 1])
+def test_saxpy_example_with_read_only_sources(kernel_id):
+    """The same example built with -DCUDADMA_SOURCES_READ_ONLY (staged loads of global memory take the
+    read-only data path, so the compiler may start them before the handshake's wait): same bits."""
+    ro = os.path.join(ROOT, "oracle", "_ref", "libv1saxpy_ours_ro.so")
+    ref = os.path.join(ROOT, "oracle", "_ref", V1_LIBS["sequential"][1])
+    if not (os.path.exists(ro) and os.path.exists(ref)):
+        pytest.skip("v1 example libraries not built")
+    lib = ctypes.CDLL(ro)
+    lib.v1saxpy_elements.restype = ctypes.c_longlong
+    n = lib.v1saxpy_elements()
+    x = oracle.fill_uniform(n, 0x5A0 + kernel_id, 0.0, 1.0)
+    y = oracle.fill_uniform(n, 0x5B0 + kernel_id, 0.0, 1.0)
+    got, ms_ro = run_saxpy(ro, kernel_id, x, y, 0.84018773)
+    want, ms_ref = run_saxpy(ref, kernel_id, x, y, 0.84018773)
+    print("v1 sequential saxpy kernel %d: %.3f ms with read-only sources, %.3f ms on the reference header" % (kernel_id, ms_ro, ms_ref))
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
 @pytest.mark.parametrize("kernel_id", range(4))
 def test_reference_throughput_benchmark_runs_unchanged_on_this_header(kernel_id):
     """src/perf/sequential/perf_sequential.cu (non_specialized, single_buffer, double_buffer, manual_buffer,
