@@ -546,6 +546,14 @@ def run_examples():
                 g[which] = max(gbs, g.get(which, gbs))
             out["perf_sequential_" + name] = {"this_header_gbs": round(g["ours"], 1), "reference_header_gbs": round(g["ref"], 1),
                                               "ratio": round(g["ours"] / g["ref"], 3)}
+    if ex.available("libsgemv_ours.so", "libsgemv_ref.so"):
+        for v, name in enumerate(ex.SGEMV_NAMES):
+            t = {}
+            for which in ("ours", "ref", "ours", "ref"):
+                _, ms = ex.run_sgemv(which, v)
+                t[which] = min(ms, t.get(which, ms))
+            out["sgemv_" + name] = {"this_header_ms": round(t["ours"], 4), "reference_header_ms": round(t["ref"], 4),
+                                    "ratio": round(t["ref"] / t["ours"], 3)}
     if not out:
         return {"unavailable": "oracle/_ref holds no example libraries (no reference checkout at build time)"}
     out["slowest_ratio"] = min(v["ratio"] for v in out.values())   # default builds only

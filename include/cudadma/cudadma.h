@@ -772,6 +772,8 @@ __device__ __forceinline__ void staged_store(const uint4 (&v)[N], char *dst, con
 #define CUDADMA_STAGED_SEQUENTIAL_MAX 128 /* bytes per DMA thread a CudaDMASequential object may hold in registers */
 #endif
 
+struct V1Forms {}; /* tag: constructor arguments mean what they mean in the v1 header */
+
 /* Constructor arguments arrive as 0..8 ints whose meaning depends on the
  * template level; ArgList just holds them. */
 struct ArgList {
@@ -1024,7 +1026,10 @@ class CudaDMAStrided : public CudaDMA {
                 "BYTES_PER_THREAD must be a positive multiple of ALIGNMENT");
   static constexpr int LEVEL = (BYTES_PER_ELMT == 0) ? 1 : ((DMA_THREADS == 0) ? 2 : ((NUM_ELMTS == 0) ? 3 : 4));
   struct Params { int dmaID, ndma, ncomp, start, bytes, rows, sstride, dstride; };
-  __device__ __forceinline__ static Params decode(const cudadma_b200::detail::ArgList &l) {
+  /* one_stride_packs: the one-stride forms leave the destination packed (rows BYTES_PER_ELMT apart),
+   * which is what they mean in the v1 header (cudaDMA.h:1812-1840, "dst_stride == BYTES_PER_ELMT");
+   * in the v2 header the one stride serves both sides (cudaDMAv2.h:5110-5127). */
+  __device__ __forceinline__ static Params decode(const cudadma_b200::detail::ArgList &l, const bool one_stride_packs = false) {
     const int *a = l.v;
     const int n = l.n;
     Params p;
@@ -1037,7 +1042,7 @@ class CudaDMAStrided : public CudaDMA {
       else if (LEVEL <= 3) { p.bytes = BYTES_PER_ELMT; p.rows = a[k]; k += 1; }
       else { p.bytes = BYTES_PER_ELMT; p.rows = NUM_ELMTS; }
       p.sstride = a[k];
-      p.dstride = (n - k >= 2) ? a[k + 1] : p.sstride;
+      p.dstride = (n - k >= 2) ? a[k + 1] : (one_stride_packs ? p.bytes : p.sstride);
     } else {
       int k = 0;
       if (LEVEL == 1) { p.bytes = a[0]; p.rows = a[1]; k = 2; }
@@ -1045,7 +1050,7 @@ class CudaDMAStrided : public CudaDMA {
       else { p.bytes = BYTES_PER_ELMT; p.rows = NUM_ELMTS; }
       p.sstride = a[k];
       const bool two = (n - k >= 2);
-      p.dstride = two ? a[k + 1] : p.sstride;
+      p.dstride = two ? a[k + 1] : (one_stride_packs ? p.bytes : p.sstride);
       int nd = DMA_THREADS, st = 0;
       if (two) {
         if (LEVEL <= 2) { nd = a[k + 2]; st = a[k + 3]; }
@@ -1079,6 +1084,12 @@ class CudaDMAStrided : public CudaDMA {
   template <typename... I>
   __device__ __forceinline__ CudaDMAStrided(I... args)
       : CudaDMAStrided(decode(cudadma_b200::detail::make_args(args...)), 0) {
+    static_assert(sizeof...(I) >= 1, "a stride argument is required");
+  }
+  /* the v1 spelling's constructor (see cudaDMAStrided at the end of this file) */
+  template <typename... I>
+  __device__ __forceinline__ CudaDMAStrided(cudadma_b200::detail::V1Forms, I... args)
+      : CudaDMAStrided(decode(cudadma_b200::detail::make_args(args...), true), 0) {
     static_assert(sizeof...(I) >= 1, "a stride argument is required");
   }
   CUDADMA_B200_XFER_OVERLOADS(const void *__restrict__ src_ptr, src_ptr)
@@ -1491,18 +1502,36 @@ typedef CudaDMACustom cudaDMACustom;
 
 /* ------------------------------------------------------------------------- */
 /* v1 spellings (include/cudaDMA.h:644, :1977, :2891): the same classes        */
-/* without the BYTES_PER_THREAD parameter, which bounded a register staging     */
-/* buffer that does not exist here. Constructor argument orders of the v1       */
-/* forms are those of the v2 forms above (cudaDMA.h:651-653, :916-920,          */
-/* :1037-1040, :1985-1996), so kernels written for v1 (the saxpy and sgemv      */
-/* examples of the reference) name these and construct them as before.          */
+/* without the BYTES_PER_THREAD parameter. v1 moved 4 * ALIGNMENT bytes per     */
+/* thread and pass, in as many passes as the transfer needed; this header       */
+/* stages a transfer at once or not at all, so the v1 names get twice that       */
+/* budget (128 bytes per DMA thread with ALIGNMENT 16): the reference's sgemv    */
+/* example's matrix panels, 128 bytes per thread, run 1.7 x the reference header */
+/* staged and 0.48 x through bulk copies. Constructor argument orders of the v1  */
+/* forms are those of the v2 forms above (cudaDMA.h:651-653, :916-920,           */
+/* :1037-1040, :1985-1996), so kernels written for v1 (the saxpy and sgemv       */
+/* examples of the reference) name these and construct them as before.           */
 /* ------------------------------------------------------------------------- */
+#ifndef CUDADMA_V1_BYTES_PER_THREAD
+#define CUDADMA_V1_BYTES_PER_THREAD(ALIGNMENT) (8 * (ALIGNMENT))
+#endif
 template <bool DO_SYNC, int ALIGNMENT, int BYTES_PER_ELMT = 0, int DMA_THREADS = 0>
-using cudaDMASequential = CudaDMASequential<DO_SYNC, ALIGNMENT, 4 * ALIGNMENT, BYTES_PER_ELMT, DMA_THREADS>;
+using cudaDMASequential = CudaDMASequential<DO_SYNC, ALIGNMENT, CUDADMA_V1_BYTES_PER_THREAD(ALIGNMENT), BYTES_PER_ELMT, DMA_THREADS>;
+/* cudaDMAStrided is a class of its own because one constructor form means something else in v1: with
+ * ONE stride argument the destination rows are packed (BYTES_PER_ELMT apart, cudaDMA.h:1981,
+ * :1812-1840), where the v2 class uses that stride on both sides. The reference's sgemv example
+ * depends on it (src/examples/sgemv/sgemv_dma.cu:340-341: matrix panels with the matrix pitch as
+ * their one stride, into a dense shared array). */
 template <bool DO_SYNC, int ALIGNMENT, int BYTES_PER_ELMT = 0, int DMA_THREADS = 0, int NUM_ELMTS = 0>
-using cudaDMAStrided = CudaDMAStrided<DO_SYNC, ALIGNMENT, 4 * ALIGNMENT, BYTES_PER_ELMT, DMA_THREADS, NUM_ELMTS>;
+class cudaDMAStrided : public CudaDMAStrided<DO_SYNC, ALIGNMENT, CUDADMA_V1_BYTES_PER_THREAD(ALIGNMENT), BYTES_PER_ELMT, DMA_THREADS, NUM_ELMTS> {
+ public:
+  template <typename... I>
+  __device__ __forceinline__ cudaDMAStrided(I... args)
+      : CudaDMAStrided<DO_SYNC, ALIGNMENT, CUDADMA_V1_BYTES_PER_THREAD(ALIGNMENT), BYTES_PER_ELMT, DMA_THREADS, NUM_ELMTS>(
+            cudadma_b200::detail::V1Forms(), args...) {}
+};
 template <bool GATHER, bool DO_SYNC, int ALIGNMENT, int BYTES_PER_ELMT = 0, int DMA_THREADS = 0, int NUM_ELMTS = 0>
-using cudaDMAIndirect = CudaDMAIndirect<GATHER, DO_SYNC, ALIGNMENT, 4 * ALIGNMENT, BYTES_PER_ELMT, DMA_THREADS, NUM_ELMTS>;
+using cudaDMAIndirect = CudaDMAIndirect<GATHER, DO_SYNC, ALIGNMENT, CUDADMA_V1_BYTES_PER_THREAD(ALIGNMENT), BYTES_PER_ELMT, DMA_THREADS, NUM_ELMTS>;
 
 #undef CUDADMA_B200_XFER_OVERLOADS
 #endif /* CUDADMA_B200_CUDADMA_H */

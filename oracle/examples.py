@@ -14,6 +14,8 @@ R = 4
 STENCIL_NAMES = ["warp_specialized_single_buffer", "warp_specialized_double_buffer", "warp_specialized_manual_buffer",
                  "non_warp_specialized_single_buffer", "non_warp_specialized_double_buffer"]
 PERFSEQ_NAMES = ["non_specialized", "single_buffer", "double_buffer", "manual_buffer"]
+# src/examples/sgemv/sgemv_dma.cu without its BOTH_DOUBLE variant, which does not compile (:468, :479)
+SGEMV_NAMES = ["vec_single", "vec_double", "vec_manual", "both_single", "both_manual", "mat_single"]
 # the reference's default problem and tile (src/examples/stencil/params_directed.h:17-24)
 STENCIL_DEFAULT_DIMS = (960, 160, 200)
 TILE_X, TILE_Y = 32, 4
@@ -84,3 +86,26 @@ def run_perf_sequential(which, kernel_id):
     if err != 0:
         raise RuntimeError("perf_sequential kernel %d (%s header): cudaError %d" % (kernel_id, which, err))
     return gbs.value, ms.value
+
+
+def run_sgemv(which, variant):
+    """The reference's sgemv example kernel `variant` (SGEMV_NAMES) on its own problem (896 x 896, alpha = 2,
+    src/examples/sgemv/sgemv_dma.cu:72-73, 774-858). Returns (y, ms per launch)."""
+    lib = ctypes.CDLL(_path("libsgemv_%s.so" % which))
+    lib.sgemv_run.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_float)]
+    n = ctypes.c_int(0)
+    lib.sgemv_run(variant, None, ctypes.byref(n), None)
+    y = np.zeros(n.value, dtype=np.float32)
+    ms = ctypes.c_float(0)
+    err = lib.sgemv_run(variant, y.ctypes.data, ctypes.byref(n), ctypes.byref(ms))
+    if err != 0:
+        raise RuntimeError("sgemv example %s (%s header): cudaError %d" % (SGEMV_NAMES[variant], which, err))
+    return y, ms.value
+
+
+def sgemv_expected(n):
+    """What the example's own verify() computes (:756-772): every term is a small integer, so fp32 sums are exact."""
+    i = np.arange(n, dtype=np.int64)
+    a = (i[None, :] * i[:, None]) % 11          # a[j, i] = (i * j) % 11
+    x = i % 11
+    return (2 * (a * x[:, None]).sum(axis=0)).astype(np.float32)

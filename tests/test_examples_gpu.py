@@ -143,3 +143,18 @@ def test_reference_throughput_benchmark_runs_unchanged_on_this_header(kernel_id)
     print("perf_sequential %s: %.0f GB/s on this header, %.0f GB/s on the reference header"
           % (examples.PERFSEQ_NAMES[kernel_id], ours, ref))
     assert ours > 0 and ref > 0 and ms_ours > 0 and ms_ref > 0
+
+
+@pytest.mark.parametrize("variant", range(6))
+def test_reference_sgemv_example_runs_unchanged_on_this_header(variant):
+    """src/examples/sgemv/sgemv_dma.cu (v1 cudaDMASequential for the vector, cudaDMAStrided for the matrix
+    panels; single, double and manual buffering) built unmodified against both headers (oracle/ref_sgemv.cu):
+    same bits, and those are the exact product (all terms are small integers)."""
+    from oracle import examples
+    if not examples.available("libsgemv_ours.so", "libsgemv_ref.so"):
+        pytest.skip("sgemv example libraries not built")
+    got, ms_ours = examples.run_sgemv("ours", variant)
+    want, ms_ref = examples.run_sgemv("ref", variant)
+    print("sgemv %s: %.4f ms on this header, %.4f ms on the reference header" % (examples.SGEMV_NAMES[variant], ms_ours, ms_ref))
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    assert np.array_equal(got, examples.sgemv_expected(got.size))
