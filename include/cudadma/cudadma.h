@@ -768,6 +768,9 @@ __device__ __forceinline__ void staged_store(const uint4 (&v)[N], char *dst, con
   }
 }
 
+#ifndef CUDADMA_NAMED_MAX_DMA_THREADS
+#define CUDADMA_NAMED_MAX_DMA_THREADS 1024 /* staged objects with more DMA threads hand over on mbarriers */
+#endif
 #ifndef CUDADMA_STAGED_SEQUENTIAL_MAX
 #define CUDADMA_STAGED_SEQUENTIAL_MAX 128 /* bytes per DMA thread a CudaDMASequential object may hold in registers */
 #endif
@@ -889,7 +892,7 @@ class CudaDMASequential : public CudaDMA {
 #endif
   typedef cudadma_b200::detail::StagedShape<STAGED ? BYTES_PER_ELMT : 16, 1, NT> Shape;
   __device__ __forceinline__ CudaDMASequential(const Params &p, int)
-      : CudaDMA(p.dmaID, p.ndma, p.ncomp, p.start, DO_SYNC, !STAGED, STAGED), m_bytes(p.bytes), m_src(0),
+      : CudaDMA(p.dmaID, p.ndma, p.ncomp, p.start, DO_SYNC, !STAGED, STAGED && NT <= CUDADMA_NAMED_MAX_DMA_THREADS), m_bytes(p.bytes), m_src(0),
         m_staged(false) {}
 
  public:
@@ -1077,7 +1080,7 @@ class CudaDMAStrided : public CudaDMA {
   static constexpr int SB = STAGED ? BYTES_PER_ELMT : 16, SR = STAGED ? NUM_ELMTS : 1; /* staged shape */
   static constexpr bool TRUST = ALIGNMENT == 16; /* pointers and strides are what the template argument says */
   __device__ __forceinline__ CudaDMAStrided(const Params &p, int)
-      : CudaDMA(p.dmaID, p.ndma, p.ncomp, p.start, DO_SYNC, !STAGED, STAGED), m_bytes(p.bytes), m_rows(p.rows),
+      : CudaDMA(p.dmaID, p.ndma, p.ncomp, p.start, DO_SYNC, !STAGED, STAGED && NT <= CUDADMA_NAMED_MAX_DMA_THREADS), m_bytes(p.bytes), m_rows(p.rows),
         m_src_stride(p.sstride), m_dst_stride(p.dstride), m_src(0), m_staged(false) {}
 
  public:
