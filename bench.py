@@ -140,6 +140,16 @@ def max_over_ranks(x):
     return float(t.item())
 
 
+def all_ranks(x):
+    """The value of every rank, in rank order, on every rank."""
+    if not dist.is_initialized():
+        return [x]
+    t = torch.tensor([x], dtype=torch.float64, device="cuda")
+    g = [torch.zeros_like(t) for _ in range(dist.get_world_size())]
+    dist.all_gather(g, t)
+    return [float(v.item()) for v in g]
+
+
 def time_region(fn, reps):
     """Device time of `reps` calls of fn, in ms, bracketed by barrier + synchronize; max over ranks."""
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -560,6 +570,31 @@ def run_examples():
     return out
 
 
+def host_link_rate(h_in, h_out, world):
+    """Every rank copies (up to) 1 GiB of its pinned input to the device and as much from the device to its pinned
+    output, on two streams at once, all ranks together; returns the per-direction rates."""
+    n = min(h_in.numel(), 1 << 28)
+    d_up = torch.empty(n, dtype=torch.float32, device="cuda")
+    d_down = torch.zeros(n, dtype=torch.float32, device="cuda")
+    keep = h_out[:n].clone()   # the result of the end-to-end run is still needed
+    s_up, s_down = torch.cuda.Stream(), torch.cuda.Stream()
+    torch.cuda.synchronize()
+    barrier()
+    t0 = time.perf_counter()
+    with torch.cuda.stream(s_up):
+        d_up.copy_(h_in[:n], non_blocking=True)
+    with torch.cuda.stream(s_down):
+        h_out[:n].copy_(d_down, non_blocking=True)
+    torch.cuda.synchronize()
+    mine = 4 * n / (time.perf_counter() - t0) / 1e9
+    barrier()
+    h_out[:n].copy_(keep)
+    rates = all_ranks(mine)
+    return {"gbs_per_direction_per_rank": [round(r, 1) for r in rates], "gbs_per_direction_sum": round(sum(rates), 1),
+            "bytes_per_rank_and_direction": 4 * n,
+            "note": "all ranks copy host->device and device->host at the same time, pinned memory, no kernels"}
+
+
 # ------------------------------------------------------------------ the stencil job
 def calibrate_rates(world):
     """Every rank times the stencil kernel alone on a 1024 x 1024 x 256 field of its own GPU, under
@@ -777,6 +812,9 @@ def run_stencil_job(impl, args, rank, world, local, peak, peak_kind):
                    ("whole job through ShardedStencil.run_host: the slab is uploaded once, stepped %d times and "
                     "downloaded once; bytes are per rank, divided by the steps" % args.steps),
            "seconds": round(e2e_s, 4)}
+    # what the box's host links carry when every rank copies both ways at once (plain cudaMemcpyAsync of the same
+    # pinned slabs, no kernels): the bound of any end-to-end figure on this box
+    e2e["host_link"] = host_link_rate(h_in, h_out, world)
     if world == 1 and impl == "ours":
         # the overlapped host run against the plain device run on the same input, all 2^31 points
         st.load(h_in)
