@@ -838,7 +838,7 @@ def run_stencil_job(impl, args, rank, world, local, peak, peak_kind):
         "value": round(value, 2), "unit": "Gpts/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": round(per_step_ms, 4), "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "sharded 25-point stencil, grid %dx%dx%d, 32x32 tiles + radius-4 halo, "
+        "config": {"workload": "sharded 25-point stencil, grid %dx%dx%d, 64x16 tiles + radius-4 halo, "
                                "4-plane halo exchange per step" % (NX, NY, NZ),
                    "planes_per_gpu": planes if rates else NZ // world,
                    "slab_balance": ({"rates_gpts": rates, "note": "slabs cut in proportion to each GPU's stencil rate, "

@@ -3,8 +3,8 @@
  *   out = c0*u + sum_{r=1..4} c_r*(u[x-r]+u[x+r]+u[y-r]+u[y+r]+u[z-r]+u[z+r]),
  * zero outside the grid, as a z-marching kernel fed by CudaDMAHalo objects.
  *
- * One CTA owns a 32 x 32 xy tile and a run of z planes. Its DMA warp streams
- * the tile plus its radius-4 halo (40 x 40 floats, one TMA box per plane, zero
+ * One CTA owns a 64 x 16 xy tile and a run of z planes. Its DMA warp streams
+ * the tile plus its radius-4 halo (72 x 24 floats, one TMA box per plane, zero
  * fill outside the grid) into a ring of shared-memory buffers. The compute
  * threads (128) each own a 4 (x) by 2 (y) patch of the tile. Every plane is read from
  * shared memory exactly once, when it arrives, and is pushed forward into the
@@ -33,14 +33,14 @@ namespace stencil25 {
 
 constexpr int R = 4;
 #ifndef STENCIL25_TILE_Y
-#define STENCIL25_TILE_Y 32 /* 32 x 32 tile: 128 compute threads; 32 x 16 with twice the CTAs measured 6 % slower */
+#define STENCIL25_TILE_Y 16 /* 64 x 16 tile: 128 compute threads */
 #endif
 #ifndef STENCIL25_TILE_X
-#define STENCIL25_TILE_X 32 /* 64 x 16 measured within 3 % of 32 x 32, 64 x 32 (one CTA per SM) slower */
+#define STENCIL25_TILE_X 64 /* 32 x 32 measured 0.6 to 1.5 % slower; 32 x 16 with twice the CTAs 6 % slower, 64 x 32 (one CTA per SM) slower */
 #endif
 constexpr int TILE_X = STENCIL25_TILE_X, TILE_Y = STENCIL25_TILE_Y;
-constexpr int WIN_X = TILE_X + 2 * R, WIN_Y = TILE_Y + 2 * R; /* 40 x 40 */
-constexpr int PLANE_BYTES = WIN_X * WIN_Y * 4;                /* 6400 */
+constexpr int WIN_X = TILE_X + 2 * R, WIN_Y = TILE_Y + 2 * R; /* 72 x 24 */
+constexpr int PLANE_BYTES = WIN_X * WIN_Y * 4;                /* 6912 */
 constexpr int SLOTS = 2 * R + 1;                              /* 9 partial output planes */
 #ifndef STENCIL25_STAGES
 #define STENCIL25_STAGES 9 /* must divide SLOTS; nine keeps eight planes of loads in flight per CTA */
@@ -305,7 +305,7 @@ __device__ __forceinline__ bool wait_for_neighbours(const Sync &sync, const bool
   return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
-/* in_map: 3-D tensor map over the nx x ny x nz input (x fastest), box 40 x 40 x 1.
+/* in_map: 3-D tensor map over the nx x ny x nz input (x fastest), box 72 x 24 x 1.
  * Output planes [z_begin, z_end) are produced; input planes outside [0, nz) read as zero. Planes
  * of a CTA are numbered kp = 0 .. depth + 7 from (first output plane - 4); output plane kp - 8 is
  * stored at step kp.

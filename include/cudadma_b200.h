@@ -121,7 +121,7 @@ int cudadma_gather_scatter_tma(void *out, size_t out_records, const void *table,
 
 /* One step of the radius-4 25-point stencil on an nx x ny x nz fp32 grid (x
  * fastest), output planes [z_begin, z_end) only; reads outside the grid give
- * zero. 32 x 32 tiles (native; 32 x 16 portable) with their halo come in through CudaDMAHalo, z-marching.
+ * zero. 64 x 16 tiles (native; 32 x 16 portable) with their halo come in through CudaDMAHalo, z-marching.
  * The reference has no such kernel; its stencil example
  * (src/examples/stencil/cudaDMA_stencil2D.cu:60-264) is the launch replaced.
  * nx % 4 == 0; pointers 16-byte aligned; in and out must not overlap.
