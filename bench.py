@@ -33,8 +33,8 @@ NX, NY, NZ = 1024, 1024, 2048          # the sharded stencil configuration
 C4 = (512, 512, 512)                   # the single-GPU stencil configuration
 BYTES_PER_POINT = 8                    # one fp32 read + one fp32 write per point and step
 # DRAM bytes per point of stencil25::tensor_kernel: dram__bytes_read + dram__bytes_write of an ncu capture
-# of the 512^3 case (1046.4 MB per launch; summary under profiles/), which grows in proportion to the points
-STENCIL_DRAM_BYTES_PER_POINT = 1046.4e6 / 512 ** 3
+# of the 512^3 case (1042.4 MB per launch; summary under profiles/), which grows in proportion to the points
+STENCIL_DRAM_BYTES_PER_POINT = 1042.4e6 / 512 ** 3
 L2_FLUSH_BYTES = 256 << 20
 EXCHANGE = "p2p"                       # halo exchange of this repository's arm at N > 1 (--exchange)
 P2P_SIGNAL = None                      # who publishes a rank's step count in that exchange (--p2p-signal; None: library default)
